@@ -55,6 +55,7 @@ class RunEntry:
     layer: int
     cache_of: Optional[int] = None
     before: Optional[str] = None       # name of a junction (`ModelSpec.junctions`) that rewrites the residual first
+    after: Optional[str] = None        # name of a junction that rewrites the residual when the entry's layer has run
 
 
 @dataclass(frozen=True)
@@ -86,7 +87,9 @@ class ModelSpec:
                 raise ValueError(f"run_order[{i}] names layer {e.layer} of {len(self.layers)}")
             if e.before is not None and e.before not in dict(self.junctions):
                 raise ValueError(f"run_order[{i}].before names the junction '{e.before}', which the spec does not have")
-            if e.before is not None and self.residual_streams != 1:
+            if e.after is not None and e.after not in dict(self.junctions):
+                raise ValueError(f"run_order[{i}].after names the junction '{e.after}', which the spec does not have")
+            if (e.before is not None or e.after is not None) and self.residual_streams != 1:
                 raise ValueError("a junction rewrites the one residual; it does not combine with several streams")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i:

@@ -240,8 +240,20 @@ struct QkvPrepParams {
   const int* page_table; int max_blocks; int page_size;
   const int* token_seq; const int* token_pos; const int* seq_slot;
   int n_heads, n_kv_heads, head_dim, v_dim, write_kv;
-  int head_norm;                         // a weightless RMS norm (norm_eps) of every q and k head, after the rotation
+  int head_norm;                         // 1: a weightless RMS norm (norm_eps) of every q and k head, after the rotation;
+                                         // 2: an RMS norm of every q and k head before the rotation, times q_norm / k_norm
+                                         //    ([head_dim] each, shared by the heads; null: no weight)
+  int interleaved;                       // the rotation pairs elements (2i, 2i + 1) instead of (i, i + rot_dims / 2)
+  float* v_first; long v_first_stride;   // value mixing (float32 [T, NKV DV]): v_mix_mode 1 stores this layer's values
+  const void* v_mix; int v_mix_dtype;    // there; 2 writes v <- (1 - m) v + m v_first[t] with the one number m = *v_mix
+  int v_mix_mode;
 };
+
+// which element a rotated element d is paired with, whether it is the pair's first, and the pair's frequency index
+__device__ __forceinline__ void rot_pair(int d, int half, int interleaved, bool& first, int& other, int& f) {
+  if (interleaved) { first = !(d & 1); other = d ^ 1; f = d >> 1; }
+  else { first = d < half; other = first ? d + half : d - half; f = first ? d : d - half; }
+}
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
@@ -280,15 +292,16 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   const int half = p.rot_dims >> 1;
   float* rot_s = row_s + nq + nk;                        // head_norm: the rotated row, then one factor per head
   float* inv_s = rot_s + nq + nk;
-  if (p.head_norm) {
+  if (p.head_norm == 1) {
     for (int i = tid; i < nq + nk; i += blockDim.x) {
       const int e = i < nq ? i : i - nq, d = e % D;
       float x = row_s[i];
       if (p.inv_freq && d < p.rot_dims) {
-        const bool first = d < half;
-        const float other = first ? row_s[i + half] : row_s[i - half];
+        bool first; int od, f;
+        rot_pair(d, half, p.interleaved, first, od, f);
+        const float other = row_s[i - d + od];
         float sn, cs;
-        sincosf((float)pos * p.inv_freq[first ? d : d - half], &sn, &cs);
+        sincosf((float)pos * p.inv_freq[f], &sn, &cs);
         x = first ? x * cs - other * sn : x * cs + other * sn;
       }
       rot_s[i] = x;
@@ -310,6 +323,41 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
       else reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)(e / D) * p.page_size) * D + e % D] = from_f32<TO>(x);
     }
   }
+  if (p.head_norm == 2) {
+    // every head by its own root mean square, times the weight of its element, and then the rotation
+    float* inv_h = row_s + nq + nk;
+    const int n_heads_all = (nq + nk) / D, warp = tid >> 5, lane = tid & 31;
+    for (int hd = warp; hd < n_heads_all; hd += blockDim.x >> 5) {
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) ss = fmaf(row_s[hd * D + d], row_s[hd * D + d], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) inv_h[hd] = 1.0f / sqrtf(ss / (float)D + p.norm_eps);
+    }
+    __syncthreads();
+    for (int i = tid; i < nq + nk; i += blockDim.x) {
+      const bool is_q = i < nq;
+      const int e = is_q ? i : i - nq;
+      const int hd = e / D, d = e % D;
+      const void* nw = is_q ? p.q_norm : p.k_norm;
+      const float inv = inv_h[i / D];
+      auto normed = [&](int idx, int el) {
+        float x = row_s[idx] * inv;
+        if (nw) x *= load_any(nw, p.norm_dtype, el);
+        return x;
+      };
+      float x = normed(i, d);
+      if (p.inv_freq && d < p.rot_dims) {
+        bool first; int od, f;
+        rot_pair(d, half, p.interleaved, first, od, f);
+        const float other = normed(i - d + od, od);
+        float sn, cs;
+        sincosf((float)pos * p.inv_freq[f], &sn, &cs);
+        x = first ? x * cs - other * sn : x * cs + other * sn;
+      }
+      if (is_q) reinterpret_cast<TO*>(p.q_out)[(size_t)t * nq + i] = from_f32<TO>(x);
+      else reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)hd * p.page_size) * D + d] = from_f32<TO>(x);
+    }
+  }
   for (int i = tid; i < (p.head_norm ? 0 : nq + nk); i += blockDim.x) {
     const bool is_q = i < nq;
     const int e = is_q ? i : i - nq;
@@ -323,9 +371,9 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
     };
     float x = normed(i, e);
     if (p.inv_freq && d < p.rot_dims) {
-      const bool first = d < half;
-      const int f = first ? d : d - half;
-      const float other = first ? normed(i + half, e + half) : normed(i - half, e - half);
+      bool first; int od, f;
+      rot_pair(d, half, p.interleaved, first, od, f);
+      const float other = normed(i - d + od, e - d + od);
       float sn, cs;
       sincosf((float)pos * p.inv_freq[f], &sn, &cs);
       x = first ? x * cs - other * sn : x * cs + other * sn;
@@ -339,6 +387,12 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   for (int i = tid; i < nv; i += blockDim.x) {
     float x = to_f32(src[nq + nk + i]);
     if (p.bias) x += load_any(p.bias, p.bias_dtype, nq + nk + i);
+    if (p.v_mix_mode == 1) {
+      p.v_first[(size_t)t * p.v_first_stride + i] = x;
+    } else if (p.v_mix_mode == 2) {
+      const float m = load_any(p.v_mix, p.v_mix_dtype, 0);
+      x = (1.0f - m) * x + m * p.v_first[(size_t)t * p.v_first_stride + i];
+    }
     reinterpret_cast<TO*>(p.v_cache)[(kv_row + (size_t)(i / DV) * p.page_size) * DV + i % DV] = from_f32<TO>(x);
   }
 }
@@ -364,12 +418,14 @@ __device__ __forceinline__ int window_low(int kind, int size, int pos) {
 }
 
 constexpr int ATT_NT = 128;
+constexpr int ATT_MAX_DIM = 640;                 // the largest key or value row: ATT_ACC accumulators per thread
+constexpr int ATT_ACC = ATT_MAX_DIM / ATT_NT;
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float q_s[256];
+  __shared__ float q_s[ATT_MAX_DIM];
   __shared__ float p_s[ATT_NT];
   __shared__ size_t off_s[ATT_NT];
   __shared__ float scratch[32];
@@ -386,7 +442,10 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
   const int* table = p.page_table + (size_t)slot * p.max_blocks;
 
   // a sink is a key without a value whose score is sink[h], unscaled: the running maximum and sum start from it
-  float m_run = -INFINITY, l_run = 0.f, acc0 = 0.f, acc1 = 0.f;
+  float m_run = -INFINITY, l_run = 0.f;
+  float acc[ATT_ACC];
+#pragma unroll
+  for (int a = 0; a < ATT_ACC; ++a) acc[a] = 0.f;
   if (p.sink) { m_run = p.sink[h]; l_run = 1.0f; }
   __syncthreads();
   // the keys a query sees: the kept first positions that lie below the window, then the window
@@ -412,12 +471,14 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
     const float l_tile = block_sum(e, scratch);       // its barriers also publish p_s and off_s
     const float alpha = expf(m_run - m_new);
     const int nv = min(ATT_NT, n_keys - base);
-    acc0 *= alpha; acc1 *= alpha;
+#pragma unroll
+    for (int a = 0; a < ATT_ACC; ++a) acc[a] *= alpha;
     for (int j = 0; j < nv; ++j) {
       const T* vr = vc + off_s[j] * DV;
       const float pj = p_s[j];
-      if (tid < DV) acc0 = fmaf(pj, to_f32(vr[tid]), acc0);
-      if (tid + ATT_NT < DV) acc1 = fmaf(pj, to_f32(vr[tid + ATT_NT]), acc1);
+#pragma unroll
+      for (int a = 0; a < ATT_ACC; ++a)
+        if (tid + a * ATT_NT < DV) acc[a] = fmaf(pj, to_f32(vr[tid + a * ATT_NT]), acc[a]);
     }
     l_run = l_run * alpha + l_tile;
     m_run = m_new;
@@ -425,8 +486,9 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
   }
   const float inv = 1.0f / fmaxf(l_run, 1e-20f);
   T* o = reinterpret_cast<T*>(p.out) + ((size_t)t * p.n_heads + h) * DV;
-  if (tid < DV) o[tid] = from_f32<T>(acc0 * inv);
-  if (tid + ATT_NT < DV) o[tid + ATT_NT] = from_f32<T>(acc1 * inv);
+#pragma unroll
+  for (int a = 0; a < ATT_ACC; ++a)
+    if (tid + a * ATT_NT < DV) o[tid + a * ATT_NT] = from_f32<T>(acc[a] * inv);
 }
 
 }  // namespace cpi
@@ -479,7 +541,8 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
                                int out_dtype, const int* page_table, int max_blocks, int page_size,
                                const int* token_seq, const int* token_pos, const int* seq_slot, int n_tokens,
                                int n_heads, int n_kv_heads, int head_dim, int v_dim, int write_kv, int head_norm,
-                               cudaStream_t stream) {
+                               int interleaved, float* v_first, long v_first_stride, const void* v_mix,
+                               int v_mix_dtype, int v_mix_mode, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
               "qkv_prepare: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
@@ -488,10 +551,15 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
               "qkv_prepare: %d rotated elements of a head of %d (an even number up to the head size)", rot_dims, head_dim);
   QkvPrepParams p{qkv, qkv_stride, bias, bias_dtype, q_norm, k_norm, norm_dtype, norm_whole, norm_eps, inv_freq,
                   rot_dims, q_out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos,
-                  seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv, head_norm};
+                  seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv, head_norm, interleaved, v_first,
+                  v_first_stride, v_mix, v_mix_dtype, v_mix_mode};
   CPI_REQUIRE(!(head_norm && norm_whole), "qkv_prepare: a norm over the whole projection or one per head, not both");
+  CPI_REQUIRE(head_norm >= 0 && head_norm <= 2, "qkv_prepare: unknown kind of head norm %d", head_norm);
+  CPI_REQUIRE(v_mix_mode == 0 || (v_first != nullptr && write_kv && (v_mix_mode == 1 || (v_mix_mode == 2 && v_mix))),
+              "qkv_prepare: value mixing needs the buffer of the first values (and, to mix, the mixing weight)");
   const size_t row = (size_t)(n_heads + (write_kv ? n_kv_heads : 0)) * head_dim;
-  const size_t smem = (head_norm ? 2 * row + n_heads + n_kv_heads : row) * sizeof(float);
+  const size_t smem = (head_norm == 1 ? 2 * row + n_heads + n_kv_heads : head_norm == 2 ? row + n_heads + n_kv_heads : row)
+                      * sizeof(float);
   CPI_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a q and k row of %zu bytes does not fit in shared memory", smem);
   // with few tokens the blocks are large (a few elements per thread); a prompt has blocks enough
   const int threads = n_tokens <= 2 * sm_count() ? 1024 : 256;
@@ -518,8 +586,8 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
               "attention: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
-  CPI_REQUIRE(head_dim >= 1 && head_dim <= 256 && v_dim >= 1 && v_dim <= 256,
-              "attention: head sizes %d (keys) and %d (values) are not supported (1 to 256)", head_dim, v_dim);
+  CPI_REQUIRE(head_dim >= 1 && head_dim <= ATT_MAX_DIM && v_dim >= 1 && v_dim <= ATT_MAX_DIM,
+              "attention: head sizes %d (keys) and %d (values) are not supported (1 to %d)", head_dim, v_dim, ATT_MAX_DIM);
   CPI_REQUIRE(score_bias == nullptr || n_dist > 0, "attention: a score bias table needs at least one distance");
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention: window kind %d needs a size > 0", window_kind);
   CPI_REQUIRE(n_heads <= 65535, "attention: too many heads (%d)", n_heads);

@@ -19,9 +19,10 @@ GATED_MODES = (MODE_SWIGLU, MODE_GEGLU, MODE_CLAMPED_GLU)
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
+GENERAL_ATTENTION_MAX_DIM = 640  # largest key or value row of the general attention kernel
 PREFILL_TILE_ROWS = 256          # most query rows of one sequence that a block of the prefill attention kernel takes
 
-ABI_VERSION = 3                  # what cpi_abi_version() of a matching library answers
+ABI_VERSION = 4                  # what cpi_abi_version() of a matching library answers
 
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
@@ -349,11 +350,16 @@ def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq
 
 def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *, n_heads,
                 n_kv_heads, head_dim, value_dim, bias=None, q_norm=None, k_norm=None, norm_whole=False, norm_eps=0.0,
-                inv_freq=None, rotary_dims=0, write_kv=True, head_norm=False):
+                inv_freq=None, rotary_dims=0, write_kv=True, head_norm=False, interleaved=False, v_first=None,
+                v_mix=None, v_mix_mode=0):
     """The general form of `qkv_post`, a block per token: rows [q | k | v] (float32 or the cache's dtype) get
     their bias, q and k an RMS norm over the whole projection (`norm_whole`, weights `q_norm` / `k_norm`), the
-    first `rotary_dims` elements of each head their rotation, and then (`head_norm`) every q and k head a weightless
-    RMS norm with `norm_eps`; q goes to q_out, k and v into the cache pages."""
+    first `rotary_dims` elements of each head their rotation, and then (`head_norm` True or 1) every q and k head a
+    weightless RMS norm with `norm_eps`; q goes to q_out, k and v into the cache pages.  `head_norm` 2: every q and k
+    head is normed before the rotation and multiplied by `q_norm` / `k_norm` ([head_dim], shared by the heads).
+    `interleaved`: the rotation pairs elements (2i, 2i + 1) instead of (i, i + rotary_dims / 2).  Value mixing:
+    `v_mix_mode` 1 also stores the values (float32) in `v_first` [T, kv heads * value_dim]; 2 writes
+    (1 - m) v + m v_first[t] into the cache, m the one number `v_mix` holds."""
     _need_cuda(qkv, q_out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, bias, q_norm, k_norm, inv_freq)
     _rowmajor(qkv, "qkv_prepare qkv")
     T = qkv.shape[0]
@@ -364,13 +370,86 @@ def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, 
     assert bias is None or bias.is_contiguous()
     nw = q_norm if q_norm is not None else k_norm
     assert q_norm is None or k_norm is None or q_norm.dtype == k_norm.dtype
+    _need_cuda(v_first, v_mix)
+    assert v_first is None or (v_first.dtype == torch.float32 and v_first.stride(1) == 1
+                               and v_first.shape == (T, n_kv_heads * value_dim))
+    assert v_mix is None or v_mix.numel() == 1
     _call("cpi_qkv_prepare", _p(qkv), c_int(dtype_code(qkv.dtype)), c_long(qkv.stride(0)), _p(bias),
           c_int(F32 if bias is None else dtype_code(bias.dtype)), _p(q_norm), _p(k_norm),
           c_int(F32 if nw is None else dtype_code(nw.dtype)), c_int(int(norm_whole)), c_float(norm_eps),
           _p(inv_freq), c_int(rotary_dims), _p(q_out), _p(k_cache), _p(v_cache), c_int(dtype_code(q_out.dtype)),
           _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot),
           c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(value_dim), c_int(int(write_kv)),
-          c_int(int(head_norm)), _stream())
+          c_int(int(head_norm)), c_int(int(interleaved)), _p(v_first), c_long(0 if v_first is None else v_first.stride(0)),
+          _p(v_mix), c_int(F32 if v_mix is None else dtype_code(v_mix.dtype)), c_int(int(v_mix_mode)), _stream())
+
+
+def latent_kv_write(x, norm_weight, eps, inv_freq, interleaved, cache, page_table, page_size, token_seq, token_pos,
+                    seq_slot, *, rank, rot):
+    """Per token, from float32 rows x [T, rank + rot] (a column slice allowed): the first `rank` elements RMS-normed
+    (times `norm_weight`), the last `rot` rotated by the token's position; the row goes into the page of its position
+    in `cache` [pages, 1, page_size, rank + rot]."""
+    _need_cuda(x, norm_weight, inv_freq, cache, page_table, token_seq, token_pos, seq_slot)
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and x.shape[1] == rank + rot
+    assert cache.is_contiguous() and cache.shape[-1] == rank + rot and cache.shape[-3] == 1
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == rot // 2)
+    assert norm_weight is None or (norm_weight.is_contiguous() and norm_weight.numel() == rank)
+    _call("cpi_latent_kv_write", _p(x), c_long(x.stride(0)), _p(norm_weight),
+          c_int(F32 if norm_weight is None else dtype_code(norm_weight.dtype)), c_float(eps), _p(inv_freq),
+          c_int(int(interleaved)), _p(cache), c_int(dtype_code(cache.dtype)), _p(page_table), c_int(page_table.shape[1]),
+          c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(x.shape[0]), c_int(rank), c_int(rot),
+          _stream())
+
+
+def latent_q_split(q, inv_freq, interleaved, plain, full, offsets, rows, token_pos, *, n_heads, dim, rot, rank):
+    """From float32 rows q [T, heads * (dim + rot)]: a head's first `dim` elements go to plain[head * T + t] (rows laid
+    out head by head), its last `rot`, rotated by the token's position, to full[t, head, rank : rank + rot].  Also
+    fills offsets[h] = h * T (int32 [heads + 1]) and rows[h * T + t] = t * heads + h (int32 [heads * T])."""
+    _need_cuda(q, inv_freq, plain, full, offsets, rows, token_pos)
+    T = q.shape[0]
+    assert q.dtype == torch.float32 and q.stride(1) == 1 and q.shape[1] == n_heads * (dim + rot)
+    assert plain.is_contiguous() and plain.numel() == T * n_heads * dim and plain.dtype == full.dtype
+    assert full.is_contiguous() and full.numel() == T * n_heads * (rank + rot)
+    assert offsets.dtype == torch.int32 and offsets.numel() >= n_heads + 1 and rows.dtype == torch.int32
+    assert rows.numel() >= T * n_heads
+    _call("cpi_latent_q_split", _p(q), c_long(q.stride(0)), _p(inv_freq), c_int(int(interleaved)), _p(plain), _p(full),
+          c_int(dtype_code(full.dtype)), _p(offsets), _p(rows), _p(token_pos), c_int(T), c_int(n_heads), c_int(dim),
+          c_int(rot), c_int(rank), _stream())
+
+
+def head_major_rows(x, out, *, n_heads, n):
+    """out[h * T + t, :n] = x[t, h, :n] for contiguous rows x [T, heads * in_dim]."""
+    _need_cuda(x, out)
+    T = x.shape[0]
+    in_dim = x.shape[1] // n_heads
+    assert x.is_contiguous() and out.is_contiguous() and x.dtype == out.dtype and out.numel() == T * n_heads * n
+    _call("cpi_head_major_rows", _p(x), _p(out), c_int(dtype_code(x.dtype)), c_int(T), c_int(n_heads), c_int(in_dim),
+          c_int(n), _stream())
+
+
+def gated_side_input(x, tokens, table, table_offset, gate, proj, norm_weight, eps):
+    """x[t] += rmsnorm(proj @ (gelu_tanh(gate @ x[t]) * table[tokens[t], table_offset : table_offset + n])) * norm_weight
+    in float32: x float32 [T, W] in place, gate [n, W], proj [W, n] (one dtype), table [vocab, *]."""
+    _need_cuda(x, tokens, table, gate, proj, norm_weight)
+    T, W = x.shape
+    n = gate.shape[0]
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and tokens.dtype == torch.int32
+    assert gate.is_contiguous() and proj.is_contiguous() and gate.dtype == proj.dtype
+    assert gate.shape == (n, W) and proj.shape == (W, n) and table.stride(1) == 1 and table_offset + n <= table.shape[1]
+    assert norm_weight is None or (norm_weight.is_contiguous() and norm_weight.numel() == W)
+    _call("cpi_gated_side_input", _p(x), c_long(x.stride(0)), _p(tokens), _p(table), c_int(dtype_code(table.dtype)),
+          c_long(table.stride(0)), c_int(int(table_offset)), c_int(table.shape[0]), _p(gate), _p(proj),
+          c_int(dtype_code(gate.dtype)), _p(norm_weight),
+          c_int(F32 if norm_weight is None else dtype_code(norm_weight.dtype)), c_float(eps), c_int(T), c_int(W),
+          c_int(n), _stream())
+
+
+def relu_squared(x, out):
+    """out = max(x, 0)^2: float32 rows x into rows of out's dtype (the two may be one buffer)."""
+    _need_cuda(x, out)
+    assert x.dim() == 2 and x.stride(1) == 1 and x.dtype == torch.float32 and out.shape == x.shape and out.stride(1) == 1
+    _call("cpi_relu_squared", _p(x), c_long(x.stride(0)), _p(out), c_int(dtype_code(out.dtype)), c_long(out.stride(0)),
+          c_int(x.shape[0]), c_int(x.shape[1]), _stream())
 
 
 def hc_step(x, *, y=None, mix=None, write=None, read=None, rows=None, norm_weight=None, norm_offset=0.0, eps=0.0,

@@ -165,6 +165,9 @@ class DecoderModel:
             owner = i if e.cache_of is None else e.cache_of
             view = parts_base.CacheView(cache_manager, owner, owns=e.cache_of is None)
             layer.block.run(layer, x, batch, view)
+            if e.after is not None:
+                self.ws.settle()
+                self.junctions[e.after].run(x, x0, batch)
             if self.layer_capture is not None:
                 self.ws.settle()
                 self.layer_capture.append(xs.sum(0))

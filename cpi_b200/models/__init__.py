@@ -2,3 +2,4 @@
 from . import llama4  # noqa: F401
 from . import veredra  # noqa: F401
 from . import savenex  # noqa: F401
+from . import nogapel  # noqa: F401

@@ -21,12 +21,23 @@ A mixer that uses one of them prepares q, k and v with the general kernel (`qkv_
 rows, so that a row is rounded once, after its norm and rotation.  There the weightless per-head norm comes after
 the rotation (qk_norm_order "after_rope").  A sliding window may carry `keep_first`: the sequence's first positions
 stay visible to every later query, at their own positions.
+
+Also served by the general preparation: `conv` (taps: q, k and v each pass a causal convolution over time per channel,
+directly after the projection, tensors "q_conv" / "k_conv" / "v_conv" [channels, taps]; the last taps - 1 projected
+rows of a sequence are per-slot state), `qk_norm_weight` "shared" (the per-head norm comes before the rotation and
+carries a weight [head_dim] that all heads share, tensors "q_norm" / "k_norm"), a rotation of interleaved pairs, and
+`value_mix` {"role": "first" | "later", "channel": name} (tensor "v_mix", one number m): the layer with role "first"
+leaves its values of the step's tokens in a buffer named by the channel, a "later" layer caches and attends to
+(1 - m) v + m v_first of the same token.
+
+`attend(...)` below is the choice of the attention kernel for prepared queries and a paged cache; other mixers that
+end in softmax attention over pages (`latent_attention`) call it too.
 """
 from __future__ import annotations
 
 import torch
 
-from ..cache.manager import KVRequirement
+from ..cache.manager import KVRequirement, StateRequirement
 from ..csrc import lib as K
 from ..phases import phase
 from ..weights.store import TensorReq
@@ -57,10 +68,22 @@ class AttentionMixer(Mixer):
         self.has_sink = bool(p.get("sink", False))
         rot = p["position"].get("rotary_dims") if p["position"].kind == "rope" else None
         self.rot_dims = self.d if rot is None else int(rot)
+        self.taps = None if p.get("conv") is None else int(p["conv"])
+        if self.taps is not None and not 1 <= self.taps <= 8:
+            raise ValueError(f"attention: a convolution of {self.taps} taps (supported: 1 to 8)")
+        self.norm_weight_shared = p.get("qk_norm_weight") == "shared"
+        if p.get("qk_norm_weight") not in (None, "shared"):
+            raise ValueError(f"attention: unknown qk_norm_weight '{p.get('qk_norm_weight')}'")
+        vm = p.get("value_mix")
+        if vm is not None and vm.get("role") not in ("first", "later"):
+            raise ValueError("attention: value_mix.role must be 'first' or 'later'")
+        self.value_mix = None if vm is None else (vm["role"], str(vm.get("channel", "v_first")))
         self.general = (self.bias or self.dv != self.d or self.rot_dims != self.d or self.d % 16 != 0
-                        or (bool(p.get("qk_norm", False)) and self.norm_scope == "projection"))
-        if not 1 <= self.d <= 256 or not 1 <= self.dv <= 256 or (not self.general and self.d < 16):
-            raise ValueError(f"attention: head sizes {self.d} / {self.dv} are not supported (up to 256)")
+                        or (bool(p.get("qk_norm", False)) and self.norm_scope == "projection")
+                        or self.taps is not None or self.norm_weight_shared or self.value_mix is not None)
+        limit = K.GENERAL_ATTENTION_MAX_DIM if self.general else 256
+        if not 1 <= self.d <= limit or not 1 <= self.dv <= limit or (not self.general and self.d < 16):
+            raise ValueError(f"attention: head sizes {self.d} / {self.dv} are not supported (up to {limit})")
         self.scale = float(p["softmax_scale"])
         self.position = build_part("position", p["position"])
         self.qk_norm = bool(p.get("qk_norm", False))
@@ -75,12 +98,18 @@ class AttentionMixer(Mixer):
         self.ws = workspace
         self.w_qkv = self.w_o = None
         self.rotary = self.score_bias = None
-        self.b_qkv = self.w_qnorm = self.w_knorm = self.sink = None
+        self.b_qkv = self.w_qnorm = self.w_knorm = self.sink = self.w_conv = self.w_vmix = None
         self.keep_first = int(w.get("keep_first") or 0) if self.window_kind == "sliding" else 0
         if self.keep_first < 0:
             raise ValueError(f"attention: keep_first must not be negative, not {self.keep_first}")
         head_norm = self.qk_norm and self.norm_scope == "head"
-        if self.general and (self.temperature is not None or (head_norm and self.norm_before_rope)
+        if self.norm_weight_shared and not (head_norm and self.norm_before_rope):
+            raise ValueError("attention: a per-head norm weight shared by the heads belongs to the per-head norm "
+                             "before the rotation (qk_norm, qk_norm_scope 'head', qk_norm_order 'before_rope')")
+        if self.value_mix is not None and not self.has_kv:
+            raise ValueError("attention: value mixing needs a layer that writes its own cache")
+        if self.general and (self.temperature is not None
+                             or (head_norm and self.norm_before_rope and not self.norm_weight_shared)
                              or (self.qk_norm and not head_norm and not self.norm_before_rope)):
             raise ValueError("attention: biases, a norm over the whole projection, a partial rotation or values of "
                              "another size do not combine with a per-head norm before the rotation, a whole-projection "
@@ -89,7 +118,8 @@ class AttentionMixer(Mixer):
         self.tn = {"q": a + "q_proj.weight", "k": a + "k_proj.weight", "v": a + "v_proj.weight",
                    "o": a + "o_proj.weight", "q_bias": a + "q_proj.bias", "k_bias": a + "k_proj.bias",
                    "v_bias": a + "v_proj.bias", "q_norm": a + "q_norm.weight", "k_norm": a + "k_norm.weight",
-                   "sink": a + "sinks"}
+                   "sink": a + "sinks", "q_conv": a + "q_conv.weight", "k_conv": a + "k_conv.weight",
+                   "v_conv": a + "v_conv.weight", "v_mix": a + "v_mix"}
         self.tn.update(p.get("tensor_names") or {})
         self.tn = {k: self.prefix + v for k, v in self.tn.items()}
 
@@ -110,6 +140,17 @@ class AttentionMixer(Mixer):
             reqs.append(TensorReq(self.tn["q_norm"], (self.nh * self.d,), init="ones+normal"))
             if self.has_kv:
                 reqs.append(TensorReq(self.tn["k_norm"], (self.nkv * self.d,), init="ones+normal"))
+        if self.norm_weight_shared:
+            reqs.append(TensorReq(self.tn["q_norm"], (self.d,), init="ones+normal"))
+            if self.has_kv:
+                reqs.append(TensorReq(self.tn["k_norm"], (self.d,), init="ones+normal"))
+        if self.taps is not None:
+            reqs.append(TensorReq(self.tn["q_conv"], (self.nh * self.d, self.taps), init="const:0.3+normal"))
+            if self.has_kv:
+                reqs += [TensorReq(self.tn["k_conv"], (self.nkv * self.d, self.taps), init="const:0.3+normal"),
+                         TensorReq(self.tn["v_conv"], (self.nkv * self.dv, self.taps), init="const:0.3+normal")]
+        if self.value_mix is not None:       # the first layer's number is stored too, and unused
+            reqs.append(TensorReq(self.tn["v_mix"], (), init="const:0.5"))
         if self.has_sink:
             reqs.append(TensorReq(self.tn["sink"], (self.nh,)))
         return reqs
@@ -130,6 +171,15 @@ class AttentionMixer(Mixer):
             self.w_qnorm = source.get(self.tn["q_norm"], device).to(torch.float32).contiguous()
             if self.has_kv:
                 self.w_knorm = source.get(self.tn["k_norm"], device).to(torch.float32).contiguous()
+        if self.norm_weight_shared:
+            self.w_qnorm = source.get(self.tn["q_norm"], device).to(torch.float32).contiguous()
+            if self.has_kv:
+                self.w_knorm = source.get(self.tn["k_norm"], device).to(torch.float32).contiguous()
+        if self.taps is not None:
+            names = ["q_conv"] + (["k_conv", "v_conv"] if self.has_kv else [])
+            self.w_conv = torch.cat([source.get(self.tn[n], device).to(torch.float32) for n in names], dim=0).contiguous()
+        if self.value_mix is not None and self.value_mix[0] == "later":
+            self.w_vmix = source.get(self.tn["v_mix"], device).to(torch.float32).reshape(1).contiguous()
         if self.has_sink:
             self.sink = source.get(self.tn["sink"], device).to(torch.float32).contiguous()
         self.position.prepare(device)
@@ -153,6 +203,15 @@ class AttentionMixer(Mixer):
                                  streams=(("k", self.nkv, self.d), ("v", self.nkv, self.dv)), keep_first=self.keep_first)
         return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size, keep_first=self.keep_first)
 
+    def state_requirements(self):
+        if self.taps is None:
+            return []
+        return [StateRequirement("conv", (max(self.taps - 1, 0), self.w_rows()))]
+
+    def w_rows(self) -> int:
+        """Rows of the stacked q | k | v projection (what the convolution runs over)."""
+        return self.nh * self.d + (self.nkv * (self.d + self.dv) if self.has_kv else 0)
+
     # ---- step ------------------------------------------------------------------------------------
     can_store = True          # forward(..., add=False) stores the mixer's output (float32) instead of adding it
 
@@ -166,17 +225,28 @@ class AttentionMixer(Mixer):
             qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), torch.float32)
             with phase("qkv"):
                 project(h, self.w_qkv, qkv)
-            if self.rotary is not None and self.rotary.interleaved:
-                raise ValueError("attention: the general preparation rotates pairs (i, i + n/2) only")
+            if self.taps is not None:          # the last taps - 1 projected rows of each sequence are its state
+                conv = self.ws.get("attn_qkv_conv", (T, self.w_qkv.shape[0]), torch.float32)
+                with phase("conv"):
+                    K.causal_conv(qkv, self.w_conv, None, cache.state("conv"), conv, batch, silu=False)
+                qkv = conv
+            v_first, mix_mode = None, 0
+            if self.value_mix is not None and cache.owns:
+                v_first = self.ws.get("attn_" + self.value_mix[1], (T, self.nkv * self.dv), torch.float32)
+                mix_mode = 1 if self.value_mix[0] == "first" else 2
+            head_norm = self.qk_norm and self.norm_scope == "head"
             with phase("kv_store"):
                 K.qkv_prepare(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                               batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                               value_dim=self.dv, bias=self.b_qkv, q_norm=self.w_qnorm, k_norm=self.w_knorm,
                               norm_whole=self.qk_norm and self.norm_scope == "projection",
-                              head_norm=self.qk_norm and self.norm_scope == "head", norm_eps=self.qk_norm_eps,
+                              head_norm=(2 if self.norm_weight_shared else 1) if head_norm else 0,
+                              norm_eps=self.qk_norm_eps,
                               inv_freq=None if self.rotary is None else self.rotary.inv_freq,
                               rotary_dims=self.rot_dims if self.rotary is not None else 0,
-                              write_kv=self.has_kv and cache.owns)
+                              interleaved=self.rotary is not None and self.rotary.interleaved,
+                              write_kv=self.has_kv and cache.owns, v_first=v_first, v_mix=self.w_vmix,
+                              v_mix_mode=mix_mode)
         else:
             qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), dt)
             with phase("qkv"):
@@ -196,39 +266,49 @@ class AttentionMixer(Mixer):
             project(att, self.w_o, residual, MODE_ADD if add else MODE_STORE)
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
-        wk = K.WINDOW_KINDS[self.window_kind]
-        # the tensor-core kernels add nothing to a score and take keys and values of one size
-        tensor_cores = use_tensor_core_kernels and self.score_bias is None and self.dv == self.d
-        if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
-                and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
-            # keys per sequence that the window lets through, at most (a bucketed bound: the split count
-            # then stays the same from step to step, which a captured graph needs)
-            longest = batch.ctx_bucket
-            if self.window_kind != "full":
-                kept = -(-self.keep_first // page_size) * page_size       # the kept first positions, in whole pages
-                longest = min(longest, self.window_size + page_size + kept)
-            pages = -(-longest // page_size)
-            base = batch.n_tokens * self.nkv
-            slots = K.attention_decode_blocks_per_sm(self.d) * K.sm_count()     # blocks that run at once
-            if base <= slots:
-                want = slots // base                                # one full wave and no more
-            else:
-                want = -(-4 * slots // base)                        # several waves of smaller blocks
-            n_splits = max(1, min(want, pages // 4, K.MAX_DECODE_SPLITS))    # a block takes four pages or more
-            K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
-                               batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
-                               window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits,
-                               sink=self.sink, keep_first=self.keep_first)
-            return
-        if (tensor_cores and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
-                and K.attention_prefill_supported(self.nh, self.nkv, self.d, page_size)):
-            K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
-                                batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=self.nh,
-                                n_kv_heads=self.nkv, head_dim=self.d, window_kind=wk, window_size=self.window_size,
-                                scale=self.scale, sink=self.sink, keep_first=self.keep_first)
-            return
-        K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
-                            batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
-                            window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,
-                            scale=self.scale, score_bias=self.score_bias, sink=self.sink, value_dim=self.dv,
-                            keep_first=self.keep_first)
+        attend(q, att, k_cache, v_cache, table, page_size, batch, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+               value_dim=self.dv, window_kind=self.window_kind, window_size=self.window_size, scale=self.scale,
+               sink=self.sink, keep_first=self.keep_first, score_bias=self.score_bias)
+
+
+def attend(q, att, k_cache, v_cache, table, page_size, batch, *, n_heads, n_kv_heads, head_dim, value_dim, window_kind,
+           window_size, scale, sink=None, keep_first=0, score_bias=None):
+    """Softmax attention of the step's prepared queries q [T, heads * head_dim] over a paged cache into att
+    [T, heads * value_dim]: the tensor-core kernels where they apply (bfloat16, keys and values of one size 64 or 128,
+    nothing added to the scores), the general kernel otherwise."""
+    nh, nkv, d, dv = n_heads, n_kv_heads, head_dim, value_dim
+    wk = K.WINDOW_KINDS[window_kind]
+    # the tensor-core kernels add nothing to a score and take keys and values of one size
+    tensor_cores = use_tensor_core_kernels and score_bias is None and dv == d
+    if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
+            and K.attention_decode_supported(nh, nkv, d, page_size)):
+        # keys per sequence that the window lets through, at most (a bucketed bound: the split count
+        # then stays the same from step to step, which a captured graph needs)
+        longest = batch.ctx_bucket
+        if window_kind != "full":
+            kept = -(-keep_first // page_size) * page_size       # the kept first positions, in whole pages
+            longest = min(longest, window_size + page_size + kept)
+        pages = -(-longest // page_size)
+        base = batch.n_tokens * nkv
+        slots = K.attention_decode_blocks_per_sm(d) * K.sm_count()     # blocks that run at once
+        if base <= slots:
+            want = slots // base                                # one full wave and no more
+        else:
+            want = -(-4 * slots // base)                        # several waves of smaller blocks
+        n_splits = max(1, min(want, pages // 4, K.MAX_DECODE_SPLITS))    # a block takes four pages or more
+        K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                           batch.seq_slot, n_heads=nh, n_kv_heads=nkv, head_dim=d,
+                           window_kind=wk, window_size=window_size, scale=scale, n_splits=n_splits,
+                           sink=sink, keep_first=keep_first)
+        return
+    if (tensor_cores and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
+            and K.attention_prefill_supported(nh, nkv, d, page_size)):
+        K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                            batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=nh,
+                            n_kv_heads=nkv, head_dim=d, window_kind=wk, window_size=window_size,
+                            scale=scale, sink=sink, keep_first=keep_first)
+        return
+    K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                        batch.seq_slot, n_heads=nh, n_kv_heads=nkv, head_dim=d, window_kind=wk,
+                        window_size=window_size, scale=scale, score_bias=score_bias, sink=sink, value_dim=dv,
+                        keep_first=keep_first)

@@ -2,6 +2,9 @@
 
 "pre_norm": x += mixer(norm1(x)); x += ffn(norm2(x))  (the order of src/engine/llama4_cpu_engine.cpp:300-329).
 
+"parallel_residual": h = norm1(x); x += mixer(h) + ffn(h).  One norm, and both sublayers read its output; each adds
+its result into the float32 residual.
+
 "hyper_connections": the residual is S streams x_1 .. x_S (float32 [S, T, H], all equal to the embedding output
 at the start; the final norm reads their sum).  Sublayer q (1: mixer, 2: feed-forward) reads a mixture of the
 streams and writes to all of them:
@@ -42,6 +45,22 @@ class PreNormBlock(Block):
         with phase("rmsnorm"):
             h2 = layer.feed_forward_norm(residual, batch.dtype)
         layer.feed_forward.forward(h2, residual, batch)
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(Block):
+    graph_safe = True
+
+    def __init__(self, spec, prefix="", **_):
+        super().__init__(spec, prefix)
+
+    def run(self, layer, residual, batch, cache):
+        layer.mixer_norm.ws.settle()
+        with phase("rmsnorm"):
+            h = layer.mixer_norm(residual, batch.dtype)
+        layer.mixer.forward(h, residual, batch, cache)
+        if layer.feed_forward is not None:
+            layer.feed_forward.forward(h, residual, batch)
 
 
 @register_block("hyper_connections")

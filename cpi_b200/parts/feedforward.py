@@ -20,6 +20,11 @@ moe_swiglu    params: hidden_size, num_experts, top_k, expert_size, shared_size 
               tensors: feed_forward.router.weight [E, H], feed_forward.experts.gate_up_proj [E, H, 2I],
               feed_forward.experts.down_proj [E, I, H], feed_forward.shared_expert.{gate,up,down}_proj.weight
 
+dense_mlp     params: hidden_size, intermediate_size, activation ("relu_squared": max(z, 0)^2), tensor_names (up, down):
+              down(act(up h)), no gate.  The activation acts on the float32 accumulator of the first product, so its
+              input is rounded once, after it.
+              tensors: feed_forward.{up,down}_proj.weight
+
 On load gate and up are stacked into one [2I, H] matrix, and the expert matrices are transposed to
 [E, 2I, H] and [E, H, I], so that every contraction reads its weights along the reduction axis.
 """
@@ -100,6 +105,41 @@ class DenseSwiGLU(FeedForward):
             else:
                 project(h, self.w_gate_up, a, MODE_SWIGLU if self.activation == "silu" else MODE_GEGLU)
             project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE, row_scale=scale)
+
+
+@register_feed_forward("dense_mlp")
+class DenseMLP(FeedForward):
+    graph_safe = True
+    can_store = True
+    ACTIVATIONS = ("relu_squared",)
+
+    def __init__(self, spec, prefix="", workspace=None):
+        super().__init__(spec, prefix)
+        self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
+        self.activation = spec.get("activation", "relu_squared")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: unknown activation '{self.activation}'; known: {list(self.ACTIVATIONS)}")
+        tn = {"up": "feed_forward.up_proj.weight", "down": "feed_forward.down_proj.weight"}
+        tn.update(spec.get("tensor_names") or {})
+        self.names = (prefix + tn["up"], prefix + tn["down"])
+        self.ws = workspace
+        self.w_up = self.w_down = None
+
+    def requirements(self):
+        return [TensorReq(self.names[0], (self.inter, self.hidden)), TensorReq(self.names[1], (self.hidden, self.inter))]
+
+    def load(self, source, device):
+        self.w_up = source.get(self.names[0], device).contiguous()
+        self.w_down = source.get(self.names[1], device).contiguous()
+
+    def forward(self, h, residual, batch, add=True):
+        T = h.shape[0]
+        with phase("mlp"):
+            z = self.ws.get("mlp_up", (T, self.inter), torch.float32)
+            a = self.ws.get("mlp_act", (T, self.inter), h.dtype)
+            project(h, self.w_up, z)
+            K.relu_squared(z, a)
+            project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE)
 
 
 @register_feed_forward("moe_swiglu")

@@ -3,8 +3,17 @@
 "concat_linear"  x <- W [x ; x0]: the residual and the embedding output side by side (x first) through one matrix
                  W [width, 2 width].  params: hidden_size, weight (tensor name).  The operand row is formed in the
                  activation dtype; the product accumulates in float32 and writes the float32 residual.
+
+"token_gated_input"  x <- x + rmsnorm(P (gelu_tanh(G x) * e)) * w: every token brings a small vector e of its own, the
+                 columns [offset, offset + dim) of its row in a table indexed by token id (one table may serve many
+                 layers, each with its own columns); a projection G [dim, width] of the residual gates it, P [width,
+                 dim] takes it to the model width, and the result enters the residual through an RMS norm with a plain
+                 weight w.  params: hidden_size, dim, table (tensor name), table_width, offset, gate, proj, norm
+                 (tensor names), eps.  One kernel, float32 throughout.
 """
 from __future__ import annotations
+
+import torch
 
 from ..csrc import lib as K
 from ..phases import phase
@@ -35,3 +44,44 @@ class ConcatLinear(Junction):
         with phase("junction"):
             K.concat_rows(x, x0, cat)
             project(cat, self.weight, x)
+
+
+_TABLES: dict = {}      # (source id, name, device) -> the table on the device, shared by the layers that read it
+
+
+@register_junction("token_gated_input")
+class TokenGatedInput(Junction):
+    graph_safe = True
+
+    def __init__(self, spec, prefix="", workspace=None):
+        super().__init__(spec, prefix)
+        self.hidden, self.dim = int(spec["hidden_size"]), int(spec["dim"])
+        self.offset, self.table_width = int(spec.get("offset", 0)), int(spec["table_width"])
+        self.vocab = int(spec["vocab_size"])
+        if self.offset < 0 or self.offset + self.dim > self.table_width:
+            raise ValueError(f"token_gated_input: columns {self.offset}..{self.offset + self.dim} of a table of "
+                             f"{self.table_width}")
+        self.eps = float(spec["eps"])
+        self.names = {k: prefix + spec[k] for k in ("table", "gate", "proj", "norm")}
+        self.table = self.w_gate = self.w_proj = self.w_norm = None
+
+    def requirements(self):
+        n = self.names
+        return [TensorReq(n["table"], (self.vocab, self.table_width)), TensorReq(n["gate"], (self.dim, self.hidden)),
+                TensorReq(n["proj"], (self.hidden, self.dim)), TensorReq(n["norm"], (self.hidden,), init="ones+normal")]
+
+    def load(self, source, device):
+        n = self.names
+        key = (id(source), n["table"], str(device))
+        if key not in _TABLES:
+            _TABLES.clear()                    # tables of a source loaded before are not kept alive
+            _TABLES[key] = source.get(n["table"], device).contiguous()
+        self.table = _TABLES[key]
+        gate, proj = source.get(n["gate"], device), source.get(n["proj"], device)
+        dt = torch.float32 if torch.float32 in (gate.dtype, proj.dtype) else torch.bfloat16
+        self.w_gate, self.w_proj = gate.to(dt).contiguous(), proj.to(dt).contiguous()
+        self.w_norm = source.get(n["norm"], device).to(torch.float32).contiguous()
+
+    def run(self, x, x0, batch) -> None:
+        with phase("side_input"):
+            K.gated_side_input(x, batch.tokens, self.table, self.offset, self.w_gate, self.w_proj, self.w_norm, self.eps)

@@ -34,12 +34,28 @@ def llama3_frequencies(head_dim: int, theta: float, scaling) -> np.ndarray:
     return out
 
 
+def llama3_frequencies_f64(dims: int, theta: float, scaling) -> np.ndarray:
+    """The same rule in double precision, rounded to float32 once: a frequency whose wavelength is shorter than
+    original / high is kept, one longer than original / low is divided by `factor`, and between the two
+    s = (original / wavelength - low) / (high - low) blends them, (1 - s) f / factor + s f."""
+    f = np.float64(theta) ** (-2.0 * np.arange(dims // 2, dtype=np.float64) / dims)
+    if scaling is not None:
+        orig, factor = float(scaling["original_max_position_embeddings"]), float(scaling["factor"])
+        low, high = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+        wavelength = 2.0 * np.pi / f
+        s = (orig / wavelength - low) / (high - low)
+        blended = (1.0 - s) * f / factor + s * f
+        f = np.where(wavelength < orig / high, f, np.where(wavelength > orig / low, f / factor, blended))
+    return f.astype(np.float32)
+
+
 @register_position("rope")
 class RotaryPosition(Position):
     """params: head_dim, theta, pairing ("half_split" pairs (d, d+D/2); "interleaved" pairs (2d, 2d+1)),
     scaling (None, the llama3 dictionary, or {"rope_type": "linear", "factor": f}: every frequency divided by f), rotary_dims (None: the whole head; n: only the first n elements of a
     head turn, as pairs (d, d + n/2) with frequencies theta^(-2d/n), the rest pass unchanged), frequency_math
-    ("float32": the powers as the reference computes them; "float64": in double precision, rounded once)."""
+    ("float32": the powers as the reference computes them; "float64": in double precision, rounded once, the
+    llama3 rule included)."""
     graph_safe = True
 
     def __init__(self, spec, prefix=""):
@@ -59,7 +75,9 @@ class RotaryPosition(Position):
         dims = int(spec["head_dim"]) if dims is None else int(dims)
         if dims < 2 or dims % 2 or dims > int(spec["head_dim"]):
             raise ValueError(f"rope: {dims} rotated elements of a head of {spec['head_dim']}")
-        if spec.get("frequency_math", "float32") == "float64" and sc is None:
+        if spec.get("frequency_math", "float32") == "float64" and sc is not None:
+            self.frequencies = llama3_frequencies_f64(dims, float(spec["theta"]), sc)
+        elif spec.get("frequency_math", "float32") == "float64":
             # theta^(-2d/n) / factor in double precision, rounded once
             f = np.float64(spec["theta"]) ** (-2.0 * np.arange(dims // 2, dtype=np.float64) / dims)
             self.frequencies = (f / (linear or 1.0)).astype(np.float32)
