@@ -40,6 +40,10 @@ the time of every phase and each phase's fraction of its roofline for both model
 `--workload savenex`: the Savenex design (windowed attention with kept first tokens beside a gated delta rule in every
 layer, dense and routed feed-forwards, a looped range) at two layer sizes beside Veredra's attention and
 gated-linear-attention layers at the same sizes, measured the same way.
+`--workload nogapel`: the Nogapel design (windowed attention with short convolutions and value mixing alternating with
+attention over a cached latent; norm once, mixer and squared-relu feed-forward side by side; a gated per-token input
+after every layer) at two layer sizes beside Veredra's windowed-attention layers at the same sizes, measured the
+same way.
 """
 from __future__ import annotations
 
@@ -880,6 +884,113 @@ def run_savenex(args) -> dict:
     return out
 
 
+NOGAPEL_SIZES = {
+    # width, ff, windowed attention (heads, kv heads, head size, window, taps), latent attention (heads, plain and
+    # rotated key size, value size, query rank, latent rank), elements of the per-token input: two points with the
+    # layer shapes of 1-3 B and 7-8 B parameter models
+    "w2048": dict(width=2048, ff=8192, attn=(16, 4, 128, 1024, 4), latent=(16, 128, 64, 128, 768, 512), side=64),
+    "w4096": dict(width=4096, ff=14336, attn=(32, 8, 128, 2048, 4), latent=(32, 128, 64, 128, 1536, 512), side=128),
+}
+
+
+def nogapel_config(sz: dict, vocab: int, pairs: int) -> dict:
+    """(windowed attention, latent attention) x pairs, every layer with a feed-forward and the per-token input."""
+    H, G, D, win, taps = sz["attn"]
+    lh, ld, lr, lv, qr, kr = sz["latent"]
+    mlp = {"kind": "dense", "ff": sz["ff"]}
+    pair = [{"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "conv": taps,
+                                            "v_mix": True, "mask": {"size": win},
+                                            "rot": {"base": 1e6, "dims": D, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0,
+                                                                                        "original": 8192}}}, "mlp": mlp},
+            {"type": "latent_attention", "mixer": {"heads": lh, "dim": ld, "rot_dim": lr, "vdim": lv, "q_rank": qr,
+                                                   "kv_rank": kr, "scale": (ld + lr) ** -0.5,
+                                                   "rot": {"base": 1e4, "dims": lr}}, "mlp": mlp}]
+    return {"architecture": "Nogapel", "layers": pair * pairs, "norm": {"eps": 1e-6}, "token_side": {"dim": sz["side"]},
+            "vocab": vocab, "width": sz["width"]}
+
+
+def veredra_attention_config(sz: dict, vocab: int, layers: int) -> dict:
+    """The closest model the library had: Veredra with windowed-attention layers only (a sink, a rotation of half of
+    each head) and gelu-gated feed-forwards, at the same head counts, head size, window, width and feed-forward size."""
+    H, G, D, win, _ = sz["attn"]
+    one = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5,
+                                          "rot": {"base": 1e6, "dims": D // 2}, "mask": {"size": win}},
+           "mlp": {"kind": "dense", "ff": sz["ff"]}}
+    return {"architecture": "Veredra", "layers": [one] * layers, "norm": {"eps": 1e-6}, "vocab": vocab,
+            "width": sz["width"], "logit_scale": 1.0, "logit_softcap": 30.0}
+
+
+def run_nogapel(args) -> dict:
+    """Prefill and decode of Nogapel at two layer sizes beside Veredra's windowed-attention layers at equal sizes, with
+    the time of every phase per layer that has it and each phase's share of its roofline: products by flops over the
+    measured bf16 rate in prefill and by weight bytes over the measured copy rate in decode; attention by flops / cache
+    bytes; row kernels by bytes."""
+    import torch
+
+    pk = peaks()
+    vocab, T, B, pairs = 32000, 2048, 8, 3
+    n_layers = 2 * pairs
+    g = torch.Generator().manual_seed(7)
+    toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()
+    out = {"metric": "tokens/s, Nogapel beside Veredra's attention layers at equal layer sizes (bf16, random weights)",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": {}}
+    tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    sizes = {k: v for k, v in NOGAPEL_SIZES.items() if not args.sizes or k in args.sizes.split(",")}
+    for name, sz in sizes.items():
+        W, ff = sz["width"], sz["ff"]
+        H, G, D, win, taps = sz["attn"]
+        lh, ld, lr, lv, qr, kr = sz["latent"]
+        nog = measure_config(nogapel_config(sz, vocab, pairs), vocab, T, B, toks)
+        ver = measure_config(veredra_attention_config(sz, vocab, n_layers), vocab, T, B, toks)
+        np_, nd = nog["phases_ms"]["prefill"], nog["phases_ms"]["decode_per_step"]
+        vp, vd = ver["phases_ms"]["prefill"], ver["phases_ms"]["decode_per_step"]
+
+        def frac(ms, flops=0.0, nbytes=0.0):
+            return None if not ms else round(max(flops / tf, nbytes / bw) / (ms / 1e3), 4)
+
+        def both(nm, n_work, vm, v_work, per_n, per_v=n_layers):
+            get = lambda ph, names: sum(ph.get(n, 0) for n in names)
+            res = {"nogapel": {"prefill": frac(get(np_, nm) / per_n, *n_work[0]), "decode": frac(get(nd, nm) / per_n, *n_work[1])}}
+            if vm is not None:
+                res["veredra"] = {"prefill": frac(get(vp, vm) / per_v, *v_work[0]), "decode": frac(get(vd, vm) / per_v, *v_work[1])}
+            return res
+
+        ctx = T - 64
+        keys_win = sum(min(t + 1, win) for t in range(T))
+        keys_all = T * (T + 1) // 2
+        row = kr + lr
+        attn_dec = B * min(ctx, win) * G * 2 * D * 2.0
+        # attention over the cached rows: scores over kr + lr elements, values over kr, all heads on the same rows
+        lat_flops, lat_dec_bytes = 2.0 * lh * keys_all * (row + kr), B * ctx * row * 2.0
+        a_proj = ((H + 2 * G) * D + H * D) * W
+        l_proj = (qr + row) * W + qr * lh * (ld + lr) + lh * ld * kr + lh * kr * lv + lh * lv * W
+        roof = {
+            "windowed attention (tensor-core kernels both)": both(
+                ["attention"], ((4.0 * D * H * keys_win,), (0.0, attn_dec)), ["attention"], ((4.0 * D * H * keys_win,), (0.0, attn_dec)),
+                per_n=pairs),
+            "attention over the cached latent (like kernel: the windowed attention above)": both(
+                ["latent_attention"], ((lat_flops,), (max(0.0, 2.0 * B * lh * ctx * (row + kr)), lat_dec_bytes)), None, None, per_n=pairs),
+            "mixer projections in and out": both(["qkv", "wo"], ((2.0 * T * (a_proj + l_proj),), (0.0, 2.0 * (a_proj + l_proj))),
+                                                 ["qkv", "wo"], ((2.0 * T * a_proj,), (0.0, 2.0 * a_proj)), per_n=pairs),
+            "feed-forward products (squared relu / gelu gate in the epilogue)": both(
+                ["mlp"], ((2.0 * T * 2.0 * W * ff,), (0.0, 2.0 * 2.0 * W * ff)),
+                ["mlp"], ((2.0 * T * 3.0 * W * ff,), (0.0, 2.0 * 3.0 * W * ff)), per_n=n_layers),
+            "row kernels of the mixers (convolution, head norm, rotation, value mixing, cache write / rotation and cache write)": both(
+                ["kv_store", "conv"], ((0.0, T * ((H + 2 * G) * D * (4 * 3 + 2.0) + (qr + row) * 4.0 + lh * (ld + lr) * 4.0 + lh * row * 2.0) / 2),) * 2,
+                ["kv_store"], ((0.0, T * (H + 2 * G) * D * (4 + 2.0)),) * 2, per_n=n_layers),
+            "norms and the residual (rmsnorm)": both(["rmsnorm"], ((0.0, T * (W * (4 + 2.0) + qr * (4 + 2.0) / 2)),) * 2,
+                                                     ["rmsnorm"], ((0.0, T * W * (4 + 2.0)),) * 2, per_n=n_layers, per_v=2 * n_layers),
+            "gated per-token input (no like kernel)": both(["side_input"], ((0.0, T * W * 8.0),) * 2, None, None, per_n=n_layers),
+        }
+        out["points"][name] = {"sizes": sz, "layers": n_layers, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx,
+                               "nogapel": nog, "veredra": ver, "fraction_of_roofline": roof}
+    big = out["points"][sorted(out["points"])[-1]]
+    out["value"] = big["nogapel"]["decode_tok_s"]
+    out["config"] = {"model": "Nogapel, (windowed attention, latent attention) x 3, per-token input after every layer",
+                     "global_batch": B, "seq_len": T, "parallelism": "single GPU", "l2": "weights of a step exceed the L2"}
+    return out
+
+
 def reference_arm_reason() -> str:
     """Why `--impl reference` has nothing to run, as found on this image (one line)."""
     return ("kurulav1/cpi is a CMake C++/CUDA project (no setup.py or pyproject.toml, so pip has nothing to install); "
@@ -899,7 +1010,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra", "savenex"],
+    ap.add_argument("--sizes", default="", help="--workload nogapel: a comma-separated subset of its size points")
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra", "savenex", "nogapel"],
                     default="scout24")
     ap.add_argument("--reference-root", default=os.environ.get("CPI_REFERENCE_ROOT"),
                     help="a checkout of kurulav1/cpi (for --workload cpu_baseline)")
@@ -919,6 +1031,9 @@ def main() -> int:
         return 0
     if args.workload == "savenex":
         print(json.dumps(run_savenex(args)))
+        return 0
+    if args.workload == "nogapel":
+        print(json.dumps(run_nogapel(args)))
         return 0
     if args.workload == "contexts":
         print(json.dumps(run_contexts(args)))

@@ -37,6 +37,12 @@ __device__ __forceinline__ float gate_mul(float g, float u, int act, float limit
   return __fdividef(g, 1.0f + __expf(-inner)) * u;
 }
 
+// The stored value of a product without a gate may pass an activation: 3 the square of relu, max(x, 0)^2.
+__device__ __forceinline__ float store_act(float x, int act) {
+  if (act == 3) { x = fmaxf(x, 0.f); x *= x; }
+  return x;
+}
+
 template <typename TO> struct Stage;
 template <> struct Stage<float> {
   using T = float;
@@ -111,6 +117,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
       const float s = scale ? scale[min(c + j, n_valid_t - 1)] : 1.0f;
       float x = v[j] * s;
       if (MODE == kSwiglu) x = gate_mul(x, u[j] * s, gate_act, gate_limit);
+      if (MODE == kStore) x = store_act(x, gate_act);
       v[j] = x;
     }
 #pragma unroll

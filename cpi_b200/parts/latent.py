@@ -129,7 +129,7 @@ class LatentAttentionMixer(Mixer):
             project(plain, self.w_ukT, full.view(T * H, row)[:, :rank], MODE_STORE, out_rows=rows, group_offsets=offsets,
                     n_groups=H, rows_per_group_hint=T)
         att = self.ws.get("latent_att", (T, H * row), dt)
-        with phase("attention"):
+        with phase("latent_attention"):
             attend(full, att, pages, pages, table, page_size, batch, n_heads=H, n_kv_heads=1, head_dim=row,
                    value_dim=row, window_kind="full", window_size=0, scale=self.scale, sink=self.sink)
         lat = self.ws.get("latent_att_heads", (H * T, rank), dt)            # head-major, the latent part only

@@ -170,4 +170,4 @@ def write_safetensors(path: str, tensors: dict, metadata: dict | None = None) ->
         f.write(hb)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
