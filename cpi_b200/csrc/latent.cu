@@ -16,6 +16,7 @@
 //   gated_side_input    x[t] += rmsnorm(P (gelu_tanh(G x[t]) * e[t])) * w with e[t] = table[token[t], off : off + n]:
 //                       a small per-token vector looked up by token id, gated by a projection of the residual,
 //                       projected up to the model width, normed and added.  Everything in float32.
+//   cast_rows, side_gate_act   the pieces of the same around two products on the tensor cores (bfloat16 operands).
 #include "common.cuh"
 
 namespace cpi {
@@ -135,48 +136,122 @@ struct SideParams {
   const void* table; int table_dtype; long table_stride; int table_offset; int vocab;      // [vocab, *]
   const void* gate; const void* proj; int w_dtype;       // [n, W], [W, n]
   const void* norm_w; int norm_dtype; float eps;         // [W]
-  int width, n;
+  int width, n, n_tokens;
 };
 
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// A block takes TPB consecutive tokens, so that a weight element read once serves all of them.  The order of every
+// sum of a token is the same for every TPB and every place in the block: a row does not depend on its neighbours.
+template <typename TW, int TPB>
 __global__ void __launch_bounds__(256) gated_side_input_kernel(SideParams p) {
   pdl_launch_dependents();
-  extern __shared__ float sm[];                  // x row [W], g [n]
+  extern __shared__ float sm[];                  // x rows [TPB][W], g [TPB][n]
   __shared__ float scratch[32];
   pdl_wait();
-  const int t = blockIdx.x, tid = threadIdx.x, W = p.width, n = p.n;
+  const int t0 = blockIdx.x * TPB, tid = threadIdx.x, W = p.width, n = p.n;
+  const int nt = min(TPB, p.n_tokens - t0);
   float* xs = sm;
-  float* g = sm + W;
-  float* x = p.x + (size_t)t * p.x_stride;
-  for (int i = tid; i < W; i += blockDim.x) xs[i] = x[i];
+  float* g = sm + (size_t)TPB * W;
+  const TW* gate = reinterpret_cast<const TW*>(p.gate);
+  const TW* proj = reinterpret_cast<const TW*>(p.proj);
+  for (int k = 0; k < TPB; ++k) {
+    const float* x = p.x + (size_t)(t0 + min(k, nt - 1)) * p.x_stride;
+    for (int i = tid; i < W; i += blockDim.x) xs[(size_t)k * W + i] = x[i];
+  }
   __syncthreads();
-  int tok = p.tokens[t];
-  tok = min(max(tok, 0), p.vocab - 1);           // the embedding kernel has flagged a token outside the table
   const int warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
   for (int j = warp; j < n; j += nw) {
-    float dot = 0.f;
-    for (int i = lane; i < W; i += 32) dot = fmaf(load_any(p.gate, p.w_dtype, (size_t)j * W + i), xs[i], dot);
-    dot = warp_sum(dot);
-    if (lane == 0)
-      g[j] = gelu_tanh_f(dot) * load_any(p.table, p.table_dtype, (size_t)tok * p.table_stride + p.table_offset + j);
+    float dot[TPB];
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) dot[k] = 0.f;
+    const TW* gr = gate + (size_t)j * W;
+    for (int i = lane; i < W; i += 32) {
+      const float w = to_f32(gr[i]);
+#pragma unroll
+      for (int k = 0; k < TPB; ++k) dot[k] = fmaf(w, xs[(size_t)k * W + i], dot[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) {
+      const float d = warp_sum(dot[k]);
+      if (lane == 0 && k < nt) {
+        int tok = p.tokens[t0 + k];
+        tok = min(max(tok, 0), p.vocab - 1);     // the embedding kernel has flagged a token outside the table
+        g[k * n + j] = gelu_tanh_f(d) * load_any(p.table, p.table_dtype, (size_t)tok * p.table_stride + p.table_offset + j);
+      }
+    }
   }
   __syncthreads();
-  float ss = 0.f;
+  float ss[TPB];
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) ss[k] = 0.f;
   for (int c = tid; c < W; c += blockDim.x) {
-    float y = 0.f;
-    for (int j = 0; j < n; ++j) y = fmaf(load_any(p.proj, p.w_dtype, (size_t)c * n + j), g[j], y);
-    ss = fmaf(y, y, ss);
-    xs[c] = y;                                   // a thread reads back only what it wrote
+    float y[TPB];
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) y[k] = 0.f;
+    const TW* pr = proj + (size_t)c * n;
+    int j = 0;
+    if (sizeof(TW) == 2 && n % 8 == 0) {         // rows of the projection start on 16 bytes: eight weights a load
+      for (; j < n; j += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(pr + j);
+        const __nv_bfloat16* w8 = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float w = __bfloat162float(w8[u]);
+#pragma unroll
+          for (int k = 0; k < TPB; ++k) y[k] = fmaf(w, g[k * n + j + u], y[k]);
+        }
+      }
+    }
+    for (; j < n; ++j) {
+      const float w = to_f32(pr[j]);
+#pragma unroll
+      for (int k = 0; k < TPB; ++k) y[k] = fmaf(w, g[k * n + j], y[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) {
+      ss[k] = fmaf(y[k], y[k], ss[k]);
+      xs[(size_t)k * W + c] = y[k];              // a thread reads back only what it wrote
+    }
   }
-  ss = block_sum(ss, scratch);
-  const float inv = 1.0f / sqrtf(ss / (float)W + p.eps);
-  for (int c = tid; c < W; c += blockDim.x) {
-    float y = xs[c] * inv;
-    if (p.norm_w) y *= load_any(p.norm_w, p.norm_dtype, c);
-    x[c] += y;
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) {
+    const float tot = block_sum(ss[k], scratch);
+    if (k >= nt) continue;
+    const float inv = 1.0f / sqrtf(tot / (float)W + p.eps);
+    float* x = p.x + (size_t)(t0 + k) * p.x_stride;
+    for (int c = tid; c < W; c += blockDim.x) {
+      float y = xs[(size_t)k * W + c] * inv;
+      if (p.norm_w) y *= load_any(p.norm_w, p.norm_dtype, c);
+      x[c] += y;
+    }
+  }
+}
+
+// The same in pieces, for the products on the tensor cores: out = x in another dtype, and
+// g[t, j] = gelu_tanh(z[t, j]) * table[token[t], off + j] for the float32 result z of the gate product.
+template <typename TO>
+__global__ void __launch_bounds__(256) cast_rows_kernel(const float* x, long x_stride, TO* out, int n_rows, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)n_rows * n;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f32<TO>(x[(i / n) * x_stride + i % n]);
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256) side_gate_act_kernel(const float* z, const int* tokens, const void* table,
+                                                            int table_dtype, long table_stride, int table_offset,
+                                                            int vocab, TO* out, int n_rows, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)n_rows * n;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / n, j = i % n;
+    const int tok = min(max(tokens[t], 0), vocab - 1);
+    out[i] = from_f32<TO>(gelu_tanh_f(z[i]) * load_any(table, table_dtype, (size_t)tok * table_stride + table_offset + j));
   }
 }
 
@@ -239,14 +314,53 @@ extern "C" int cpi_gated_side_input(float* x, long x_stride, const int* tokens, 
                                     int n, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(width >= 1 && n >= 1 && vocab >= 1, "gated_side_input: bad sizes width=%d n=%d vocab=%d", width, n, vocab);
-  const size_t smem = (size_t)(width + n) * sizeof(float);
-  CPI_REQUIRE(smem <= 200 * 1024, "gated_side_input: a row of %d + %d floats does not fit in shared memory", width, n);
+  const size_t row = (size_t)(width + n) * sizeof(float);
+  CPI_REQUIRE(row <= 200 * 1024, "gated_side_input: a row of %d + %d floats does not fit in shared memory", width, n);
+  // tokens a block takes: as many as fit, and no more than leave every multiprocessor a block
+  int tpb = 8;
+  while (tpb > 1 && (row * tpb > 200 * 1024 || (n_tokens + tpb - 1) / tpb < sm_count())) tpb >>= 1;
   SideParams p{x, x_stride, tokens, table, table_dtype, table_stride, table_offset, vocab, gate, proj, w_dtype,
-               norm_w, norm_dtype, eps, width, n};
-  if (smem > 48 * 1024)
-    cudaFuncSetAttribute(gated_side_input_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  cpi::launch_pdl(gated_side_input_kernel, dim3(n_tokens), dim3(256), smem, stream, p);
+               norm_w, norm_dtype, eps, width, n, n_tokens};
+  const size_t smem = row * tpb;
+  const dim3 grid((n_tokens + tpb - 1) / tpb);
+#define CPI_SIDE_LAUNCH(TW, TPB)                                                                                  \
+  do {                                                                                                            \
+    if (smem > 48 * 1024)                                                                                         \
+      cudaFuncSetAttribute(gated_side_input_kernel<TW, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    cpi::launch_pdl(gated_side_input_kernel<TW, TPB>, grid, dim3(256), smem, stream, p);                          \
+  } while (0)
+  CPI_DISPATCH_DTYPE(w_dtype, TW, {
+    if (tpb == 8) CPI_SIDE_LAUNCH(TW, 8);
+    else if (tpb == 4) CPI_SIDE_LAUNCH(TW, 4);
+    else if (tpb == 2) CPI_SIDE_LAUNCH(TW, 2);
+    else CPI_SIDE_LAUNCH(TW, 1);
+  });
+#undef CPI_SIDE_LAUNCH
   return check_launch("gated_side_input");
+}
+
+static int row_blocks(size_t total) {
+  const size_t want = (total + 255) / 256, most = (size_t)8 * sm_count();
+  return (int)(want < most ? want : most);
+}
+
+extern "C" int cpi_cast_rows(const float* x, long x_stride, void* out, int out_dtype, int n_rows, int n,
+                             cudaStream_t stream) {
+  if (n_rows == 0 || n == 0) return 0;
+  CPI_DISPATCH_DTYPE(out_dtype, T, cpi::launch_pdl(cast_rows_kernel<T>, dim3(row_blocks((size_t)n_rows * n)), dim3(256), 0,
+                                                   stream, x, x_stride, reinterpret_cast<T*>(out), n_rows, n));
+  return check_launch("cast_rows");
+}
+
+extern "C" int cpi_side_gate_act(const float* z, const int* tokens, const void* table, int table_dtype,
+                                 long table_stride, int table_offset, int vocab, void* out, int out_dtype, int n_rows,
+                                 int n, cudaStream_t stream) {
+  if (n_rows == 0 || n == 0) return 0;
+  CPI_REQUIRE(vocab >= 1 && table_offset >= 0, "side_gate_act: bad sizes vocab=%d offset=%d", vocab, table_offset);
+  CPI_DISPATCH_DTYPE(out_dtype, T, cpi::launch_pdl(side_gate_act_kernel<T>, dim3(row_blocks((size_t)n_rows * n)), dim3(256),
+                                                   0, stream, z, tokens, table, table_dtype, table_stride, table_offset,
+                                                   vocab, reinterpret_cast<T*>(out), n_rows, n));
+  return check_launch("side_gate_act");
 }
 
 extern "C" int cpi_relu_squared(const float* x, long x_stride, void* out, int out_dtype, long out_stride, int n_rows,

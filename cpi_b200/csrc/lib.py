@@ -444,6 +444,25 @@ def gated_side_input(x, tokens, table, table_offset, gate, proj, norm_weight, ep
           c_int(n), _stream())
 
 
+def cast_rows(x, out):
+    """out = x in out's dtype: float32 rows x [T, n] (a row stride allowed), out contiguous."""
+    _need_cuda(x, out)
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and out.is_contiguous() and out.shape == x.shape
+    _call("cpi_cast_rows", _p(x), c_long(x.stride(0)), _p(out), c_int(dtype_code(out.dtype)), c_int(x.shape[0]),
+          c_int(x.shape[1]), _stream())
+
+
+def side_gate_act(z, tokens, table, table_offset, out):
+    """out[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], table_offset + j]: z float32 [T, n] contiguous."""
+    _need_cuda(z, tokens, table, out)
+    T, n = z.shape
+    assert z.dtype == torch.float32 and z.is_contiguous() and out.is_contiguous() and out.shape == z.shape
+    assert tokens.dtype == torch.int32 and table.stride(1) == 1 and table_offset + n <= table.shape[1]
+    _call("cpi_side_gate_act", _p(z), _p(tokens), _p(table), c_int(dtype_code(table.dtype)), c_long(table.stride(0)),
+          c_int(int(table_offset)), c_int(table.shape[0]), _p(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(n),
+          _stream())
+
+
 def relu_squared(x, out):
     """out = max(x, 0)^2: float32 rows x into rows of out's dtype (the two may be one buffer)."""
     _need_cuda(x, out)
@@ -638,6 +657,51 @@ def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq,
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(T),
           c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale),
           c_int(n_splits), _p(po), _p(pml), _p(tc_error_flag(q.device)), c_int(int(keep_first)), _p(sink), _stream())
+
+
+def latent_attention_supported(row: int, rank: int) -> bool:
+    """Whether the tensor-core kernel of attention over cached latent rows takes rows of `row` elements whose first
+    `rank` are the value."""
+    return bool(load().cpi_latent_attention_supported(c_int(int(row)), c_int(int(rank))))
+
+
+def latent_attention_max_splits() -> int:
+    return int(load().cpi_latent_attention_max_splits())
+
+
+LATENT_KEY_TILE = 32             # cached positions that a block of the latent attention kernel takes at a time
+
+
+def latent_attention(q, out, cache, page_table, page_size, token_seq, token_pos, seq_slot, *, n_heads, rank, scale,
+                     sink=None, tile_tok0=None, tile_rows=None, n_splits=1):
+    """bfloat16 softmax attention of q [T, heads * row] over cached rows [pages, 1, page_size, row] that all heads
+    share: a row is the key, its first `rank` elements the value; a query sees every position up to its own.  out
+    [heads * T, rank] is laid out head by head (row h * T + t).  With `tile_tok0` / `tile_rows` (runs of at most
+    PREFILL_TILE_ROWS consecutive tokens of one sequence) a block takes a few tokens of a run; without, every token
+    is alone and its keys are divided over `n_splits` blocks.  `sink`: float32 [heads], joins the denominators."""
+    _need_cuda(q, out, cache, page_table, token_seq, token_pos, seq_slot, sink, tile_tok0, tile_rows)
+    T = q.shape[0]
+    row = cache.shape[-1]
+    assert q.dtype == out.dtype == cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and cache.shape[-3] == 1
+    assert q.shape[1] == n_heads * row and out.numel() == T * n_heads * rank
+    assert sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_heads)
+    assert (tile_tok0 is None) == (tile_rows is None)
+    po = pml = None
+    if n_splits > 1:
+        idx = q.device.index or 0
+        need = T * n_heads * n_splits * (rank + 2)
+        buf = _dec_scratch.get(idx)
+        if buf is None or buf.numel() < need:
+            global scratch_generation
+            buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+            _dec_scratch[idx] = buf
+            scratch_generation += 1
+        po, pml = buf, buf[T * n_heads * n_splits * rank:]
+    _call("cpi_latent_attention", _p(q), _p(cache), _p(out), _p(po), _p(pml), _p(page_table),
+          c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), _p(tile_tok0),
+          _p(tile_rows), c_int(0 if tile_tok0 is None else tile_tok0.numel()), c_int(PREFILL_TILE_ROWS), _p(sink),
+          c_int(T), c_int(n_heads), c_int(row), c_int(rank), c_int(int(n_splits)), c_float(scale), _stream())
 
 
 def attention_decode_blocks_per_sm(head_dim: int) -> int:

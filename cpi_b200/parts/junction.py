@@ -9,7 +9,9 @@
                  layers, each with its own columns); a projection G [dim, width] of the residual gates it, P [width,
                  dim] takes it to the model width, and the result enters the residual through an RMS norm with a plain
                  weight w.  params: hidden_size, dim, table (tensor name), table_width, offset, gate, proj, norm
-                 (tensor names), eps.  One kernel, float32 throughout.
+                 (tensor names), eps.  float32: one kernel, float32 throughout.  bfloat16: the two products run as
+                 matrix products with bfloat16 operands (the residual row and the gated vector are rounded for them),
+                 the activation, the norm and the sum stay float32.
 """
 from __future__ import annotations
 
@@ -46,9 +48,6 @@ class ConcatLinear(Junction):
             project(cat, self.weight, x)
 
 
-_TABLES: dict = {}      # (source id, name, device) -> the table on the device, shared by the layers that read it
-
-
 @register_junction("token_gated_input")
 class TokenGatedInput(Junction):
     graph_safe = True
@@ -63,6 +62,7 @@ class TokenGatedInput(Junction):
                              f"{self.table_width}")
         self.eps = float(spec["eps"])
         self.names = {k: prefix + spec[k] for k in ("table", "gate", "proj", "norm")}
+        self.ws = workspace
         self.table = self.w_gate = self.w_proj = self.w_norm = None
 
     def requirements(self):
@@ -72,16 +72,36 @@ class TokenGatedInput(Junction):
 
     def load(self, source, device):
         n = self.names
-        key = (id(source), n["table"], str(device))
-        if key not in _TABLES:
-            _TABLES.clear()                    # tables of a source loaded before are not kept alive
-            _TABLES[key] = source.get(n["table"], device).contiguous()
-        self.table = _TABLES[key]
+        shared = getattr(source, "_shared_tables", None)      # one copy on the device for the layers of one source
+        if shared is None:
+            shared = {}
+            try:
+                source._shared_tables = shared
+            except AttributeError:
+                pass
+        key = (n["table"], str(device))
+        if key not in shared:
+            shared[key] = source.get(n["table"], device).contiguous()
+        self.table = shared[key]
         gate, proj = source.get(n["gate"], device), source.get(n["proj"], device)
         dt = torch.float32 if torch.float32 in (gate.dtype, proj.dtype) else torch.bfloat16
         self.w_gate, self.w_proj = gate.to(dt).contiguous(), proj.to(dt).contiguous()
         self.w_norm = source.get(n["norm"], device).to(torch.float32).contiguous()
 
     def run(self, x, x0, batch) -> None:
+        T = x.shape[0]
         with phase("side_input"):
-            K.gated_side_input(x, batch.tokens, self.table, self.offset, self.w_gate, self.w_proj, self.w_norm, self.eps)
+            if batch.dtype != torch.bfloat16 or self.w_gate.dtype != torch.bfloat16:
+                K.gated_side_input(x, batch.tokens, self.table, self.offset, self.w_gate, self.w_proj, self.w_norm,
+                                   self.eps)
+                return
+            # bfloat16: the two products on the tensor cores, the gate's activation and the norm in float32 between
+            xb = self.ws.get("side_x", (T, self.hidden), torch.bfloat16)
+            z = self.ws.get("side_z", (T, self.dim), torch.float32)
+            g = self.ws.get("side_g", (T, self.dim), torch.bfloat16)
+            y = self.ws.get("side_y", (T, self.hidden), torch.float32)
+            K.cast_rows(x, xb)
+            project(xb, self.w_gate, z)
+            K.side_gate_act(z, batch.tokens, self.table, self.offset, g)
+            project(g, self.w_proj, y)
+            K.branch_norm_sum([y], [self.w_norm], x, eps=self.eps, add=True)

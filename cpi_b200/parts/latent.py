@@ -26,9 +26,15 @@ from ..cache.manager import KVRequirement
 from ..csrc import lib as K
 from ..phases import phase
 from ..weights.store import TensorReq
+from . import attention as _attention
 from .attention import attend
 from .base import Mixer, RotaryEncoding, build_part, register_mixer
 from .linear import MODE_ADD, MODE_STORE, project
+
+
+def use_tensor_core_kernels() -> bool:
+    """The switch of the attention part: off, every attention runs through the general kernel."""
+    return _attention.use_tensor_core_kernels
 
 
 @register_mixer("latent_attention")
@@ -128,14 +134,31 @@ class LatentAttentionMixer(Mixer):
         with phase("qkv"):               # the plain part of every query through its head's W_uk^T, into full[t, head, :rank]
             project(plain, self.w_ukT, full.view(T * H, row)[:, :rank], MODE_STORE, out_rows=rows, group_offsets=offsets,
                     n_groups=H, rows_per_group_hint=T)
-        att = self.ws.get("latent_att", (T, H * row), dt)
-        with phase("latent_attention"):
-            attend(full, att, pages, pages, table, page_size, batch, n_heads=H, n_kv_heads=1, head_dim=row,
-                   value_dim=row, window_kind="full", window_size=0, scale=self.scale, sink=self.sink)
         lat = self.ws.get("latent_att_heads", (H * T, rank), dt)            # head-major, the latent part only
         out = self.ws.get("latent_values", (T, H * self.dv), dt)
+        if use_tensor_core_kernels() and dt == torch.bfloat16 and K.latent_attention_supported(row, rank):
+            with phase("latent_attention"):
+                if batch.is_decode:
+                    # key splits from a bucketed bound of the context, so that a captured graph keeps its shape
+                    groups = -(-H // 64)
+                    tiles = -(-batch.ctx_bucket // K.LATENT_KEY_TILE)
+                    n_splits = max(1, min(K.sm_count() // max(1, T * groups), tiles // 4,
+                                          K.latent_attention_max_splits()))
+                    K.latent_attention(full, lat, pages, table, page_size, batch.token_seq, batch.token_pos,
+                                       batch.seq_slot, n_heads=H, rank=rank, scale=self.scale, sink=self.sink,
+                                       n_splits=n_splits)
+                else:
+                    K.latent_attention(full, lat, pages, table, page_size, batch.token_seq, batch.token_pos,
+                                       batch.seq_slot, n_heads=H, rank=rank, scale=self.scale, sink=self.sink,
+                                       tile_tok0=batch.tile_tok0, tile_rows=batch.tile_rows)
+        else:
+            att = self.ws.get("latent_att", (T, H * row), dt)
+            with phase("latent_attention"):
+                attend(full, att, pages, pages, table, page_size, batch, n_heads=H, n_kv_heads=1, head_dim=row,
+                       value_dim=row, window_kind="full", window_size=0, scale=self.scale, sink=self.sink)
+            with phase("wo"):
+                K.head_major_rows(att, lat, n_heads=H, n=rank)
         with phase("wo"):
-            K.head_major_rows(att, lat, n_heads=H, n=rank)
             project(lat, self.w_uv, out.view(T * H, self.dv), MODE_STORE, out_rows=rows, group_offsets=offsets,
                     n_groups=H, rows_per_group_hint=T)
             project(out, self.w_o, residual, MODE_ADD if add else MODE_STORE)

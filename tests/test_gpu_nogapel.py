@@ -275,6 +275,46 @@ def test_gated_token_input_kernel(T, W, n, off, wdt):
         assert (P.token_side_input(x.double(), toks, pw, "p.", layer, n, 1e-5) - want).abs().max() < 1e-9
 
 
+@pytest.mark.parametrize("T,W,n,layer,dtype", [(5, 52, 6, 2, "bfloat16"), (600, 256, 64, 1, "bfloat16"),
+                                               (9, 128, 16, 0, "bfloat16"), (4, 40, 3, 1, "float32")])
+def test_gated_token_input_part_in_both_precisions(T, W, n, layer, dtype):
+    """The junction as the model runs it: float32 in one kernel, bfloat16 with its two products as matrix products
+    (few and many tokens, sizes the tensor-core kernels take and sizes they do not); two parts share one table."""
+    from cpi_b200.config.spec import PartSpec
+    from cpi_b200.parts.base import build_part
+    from cpi_b200.parts.workspace import Workspace
+    from cpi_b200.weights.store import DictSource
+    dt = getattr(torch, dtype)
+    g = torch.Generator().manual_seed(T * W)
+    vocab, n_layers = 30, 3
+    x = rn(g, T, W, std=2.0)
+    table = rn(g, vocab, n_layers * n).bfloat16()
+    gate, proj = rn(g, n, W, std=1.5 * W ** -0.5).bfloat16(), rn(g, W, n, std=n ** -0.5).bfloat16()
+    nw = rn(g, W, std=0.3, mean=0.8).bfloat16()
+    toks = torch.randint(0, vocab, (T,), generator=g)
+    src = DictSource({"side.embed": table, "p.gate": gate, "p.proj": proj, "p.norm": nw,
+                      "o.gate": gate, "o.proj": proj, "o.norm": nw})
+    ws = Workspace(torch.device(DEV))
+    spec = {"hidden_size": W, "vocab_size": vocab, "dim": n, "table": "side.embed", "table_width": n_layers * n,
+            "offset": layer * n, "gate": "p.gate", "proj": "p.proj", "norm": "p.norm", "eps": 1e-5}
+    part = build_part("junction", PartSpec("token_gated_input", spec), "", workspace=ws)
+    other = build_part("junction", PartSpec("token_gated_input", {**spec, "offset": 0, "gate": "o.gate", "proj": "o.proj",
+                                                                  "norm": "o.norm"}), "", workspace=ws)
+    part.load(src, torch.device(DEV))
+    other.load(src, torch.device(DEV))
+    assert part.table.data_ptr() == other.table.data_ptr()
+
+    class B:
+        tokens = toks.to(torch.int32).to(DEV)
+    B.dtype = dt
+    buf = x.to(DEV).clone()
+    part.run(buf, None, B)
+    pw = {"side.embed": table.double(), "p.gate": gate.double(), "p.proj": proj.double(), "p.norm": nw.double()}
+    want = P.token_side_input(x.double(), toks, pw, "p.", layer, n, 1e-5)
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    assert (buf.cpu().double() - want).abs().max() < tol * want.abs().max()
+
+
 @pytest.mark.parametrize("T,I,H,dtype", [(5, 44, 52, torch.float32), (40, 200, 136, torch.bfloat16),
                                          (600, 256, 128, torch.bfloat16), (7, 96, 64, torch.bfloat16)])
 def test_squared_relu_feed_forward_part(T, I, H, dtype):
@@ -367,6 +407,62 @@ def test_a_far_row_and_the_sink_in_attention_over_shared_rows(row, heads, dtype)
             assert (got[1] - want).abs().max() < 2e-2, (n_q, use_sink)
             flat = rows.to(dtype).float().mean(0)
             assert (got[0] - flat).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("H,row,rank", [(6, 128, 96), (16, 576, 512), (80, 48, 32), (5, 208, 192), (3, 16, 16)])
+def test_tensor_core_attention_over_shared_rows_against_plain_softmax(H, row, rank):
+    """The kernel that stacks the heads of a few tokens into one tile, against softmax in float64 over the same
+    rounded rows: sequences that start at zero and in the middle, at page and key-tile borders, in scattered pages; one
+    token per sequence with the keys undivided and divided over blocks; with and without a sink; more heads than a tile
+    has rows."""
+    lib = K()
+    assert lib.latent_attention_supported(row, rank)
+    page, n_pages = 16, 64
+    g = torch.Generator().manual_seed(H * row)
+    perm = torch.randperm(n_pages, generator=g)
+    table = torch.stack([perm[:20], perm[20:40], perm[40:60]]).to(torch.int32).to(DEV)       # slots 0, 1, 2
+    lens = [257, 96, 320]
+    seqs = [rn(g, n, row, std=0.7).bfloat16() for n in lens]
+    cache = torch.full((n_pages, 1, page, row), float("nan"), dtype=torch.bfloat16, device=DEV)
+    for s, rows in enumerate(seqs):
+        for pos in range(rows.shape[0]):
+            cache[int(table[s, pos // page]), 0, pos % page] = rows[pos]
+    scale = 1.7 / row ** 0.5
+    sink = rn(g, H).to(DEV)
+
+    def want(q, slots, starts, n_new, snk):
+        out, t = torch.zeros(H * q.shape[0], rank, dtype=F64), 0
+        for s, st, n in zip(slots, starts, n_new):
+            for i in range(n):
+                keys = seqs[s][:st + i + 1].double()
+                sc = q[t].double().view(H, row) @ keys.T * scale
+                if snk is not None:
+                    sc = torch.cat([sc, snk.double().cpu()[:, None]], 1)
+                w = torch.softmax(sc, -1)[:, :keys.shape[0]]
+                out[torch.arange(H) * q.shape[0] + t] = w @ keys[:, :rank]
+                t += 1
+        return out
+
+    cases = [([0, 1, 2], [0, 33, 63], [250, 40, 1], None),          # runs: from zero, from the middle, a single token
+             ([2, 0], [200, 31], [120, 2], None),
+             ([0, 1, 2], [256, 0, 319], [1, 1, 1], 1),              # one token each, keys undivided
+             ([0, 1, 2], [128, 95, 300], [1, 1, 1], 4),             # keys over four blocks (some get nothing)
+             ([1], [31], [1], 7)]
+    for slots, starts, n_new, splits in cases:
+        b = FakeBatch(slots, starts, n_new)
+        T = sum(n_new)
+        q = rn(g, T, H * row).bfloat16()
+        for snk in (None, sink):
+            out = torch.full((H * T, rank), float("nan"), dtype=torch.bfloat16, device=DEV)
+            kw = {}
+            if splits is None:
+                kw = {"tile_tok0": b.seq_tok0, "tile_rows": b.seq_new}
+            else:
+                kw = {"n_splits": splits}
+            lib.latent_attention(q.to(DEV), out, cache, table, page, b.token_seq, b.token_pos, b.seq_slot, n_heads=H,
+                                 rank=rank, scale=scale, sink=snk, **kw)
+            ref = want(q, slots, starts, n_new, snk)
+            assert (out.double().cpu() - ref).abs().max() < 2e-2, (slots, starts, n_new, splits, snk is not None)
 
 
 # ---- the model -------------------------------------------------------------------------------------------
