@@ -8,8 +8,9 @@
 //   S = Q K^T         8 warps: warp (g, c) owns query rows [16 g, 16 g + 16) and key columns [16 c, 16 c + 16) of
 //                     the tile; fragments through ldmatrix from padded shared-memory rows; S * scale * log2(e),
 //                     masked by position, goes to shared memory in float32
-//   P = 2^(S - m)     each warp for its 16 rows (the two warps of a row group compute the same numbers): running
-//                     maximum and sum in float32, P rounded to bfloat16 as the A operand
+//   P = 2^(S - m)     each warp for its 16 rows (the two warps of a row group compute the same numbers, after a
+//                     barrier of their own): running maximum and sum in float32, P rounded to bfloat16 as the A
+//                     operand; the accumulators are rescaled only when a maximum of the warp's rows has grown
 //   O += P V          warp (g, c) accumulates rows [16 g, +16) x value columns [c * CH, (c + 1) * CH) in registers
 //                     (CH = 8 NT, NT = 8, 16 or 32 by the latent's size); V fragments through ldmatrix.trans
 //                     from the same shared-memory tile that held the keys
@@ -67,7 +68,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NT>
+template <int NT, bool FULL>
 __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) {
   pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -149,17 +150,38 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) 
     const __nv_bfloat16* KV = KVs + (size_t)buf * BN * LD;
     const int kv0 = it * BN;
     if (active) {
+      // two k-steps a turn on accumulators of their own (four independent chains), the fragments of the next
+      // turn loaded before the products of this one
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       const __nv_bfloat16* qa = Qs + (size_t)(rg * 16 + (lane & 15)) * LD + (lane >> 4) * 8;
       const __nv_bfloat16* kb = KV + (size_t)(ch * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + ((lane >> 3) & 1) * 8;
-#pragma unroll 4
-      for (int kk = 0; kk < row; kk += 16) {
-        uint32_t a[4], b[4];
-        ldsm_x4(a, qa + kk);
-        ldsm_x4(b, kb + kk);
-        mma_bf16(s[0], a, b[0], b[1]);
-        mma_bf16(s[1], a, b[2], b[3]);
+      uint32_t a0[4], b0[4], a1[4], b1[4];
+      const int pairs_end = row & ~31;
+      if (pairs_end > 0) {
+        ldsm_x4(a0, qa); ldsm_x4(b0, kb);
+        ldsm_x4(a1, qa + 16); ldsm_x4(b1, kb + 16);
       }
+#pragma unroll 2
+      for (int kk = 0; kk < pairs_end; kk += 32) {
+        uint32_t na0[4], nb0[4], na1[4], nb1[4];
+        const int nk = kk + 32 < pairs_end ? kk + 32 : kk;        // the last turn loads its own again (unused)
+        ldsm_x4(na0, qa + nk); ldsm_x4(nb0, kb + nk);
+        mma_bf16(s[0], a0, b0[0], b0[1]);
+        mma_bf16(s[1], a0, b0[2], b0[3]);
+        ldsm_x4(na1, qa + nk + 16); ldsm_x4(nb1, kb + nk + 16);
+        mma_bf16(s2[0], a1, b1[0], b1[1]);
+        mma_bf16(s2[1], a1, b1[2], b1[3]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) { a0[u] = na0[u]; b0[u] = nb0[u]; a1[u] = na1[u]; b1[u] = nb1[u]; }
+      }
+      if (pairs_end < row) {                                       // an odd number of k-steps: the last one
+        ldsm_x4(a0, qa + pairs_end); ldsm_x4(b0, kb + pairs_end);
+        mma_bf16(s[0], a0, b0[0], b0[1]);
+        mma_bf16(s[1], a0, b0[2], b0[3]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { s[0][u] += s2[0][u]; s[1][u] += s2[1][u]; }
       const int r0 = rg * 16 + g, qp0 = qpos_s[r0], qp1 = qpos_s[r0 + 8];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
@@ -173,8 +195,9 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) 
         *reinterpret_cast<float2*>(Ss + (r0 + 8) * SLD + col) = v1;
       }
     }
-    __syncthreads();
     if (active) {
+      // the scores of 16 rows pass between the two warps of the row group only: a barrier of their own
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + rg) : "memory");
       uint32_t pa[BN / 16][4];
       float alpha[2];
 #pragma unroll
@@ -202,21 +225,34 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) 
         }
         l_run[hrow] = l_run[hrow] * alpha[hrow] + sum;
       }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {      // a maximum of the warp's rows has grown
 #pragma unroll
-      for (int i = 0; i < NT; ++i) {
-        o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-        o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        for (int i = 0; i < NT; ++i) {
+          o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+          o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
       }
 #pragma unroll
       for (int ks = 0; ks < BN / 16; ++ks) {
         const __nv_bfloat16* vb = KV + (size_t)(ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LD + col_base + (lane >> 4) * 8;
+        if (FULL) {                          // every column of the warp is a value column: nothing to ask per pair
+          uint32_t b[2][4];
+          ldsm_x4_trans(b[0], vb);
 #pragma unroll
-        for (int i = 0; i < NT; i += 2) {
-          if (col_base + i * 8 < rank) {
-            uint32_t b[4];
-            ldsm_x4_trans(b, vb + i * 8);
-            mma_bf16(o[i], pa[ks], b[0], b[1]);
-            mma_bf16(o[i + 1], pa[ks], b[2], b[3]);
+          for (int i = 0; i < NT; i += 2) {
+            if (i + 2 < NT) ldsm_x4_trans(b[((i >> 1) + 1) & 1], vb + (i + 2) * 8);
+            mma_bf16(o[i], pa[ks], b[(i >> 1) & 1][0], b[(i >> 1) & 1][1]);
+            mma_bf16(o[i + 1], pa[ks], b[(i >> 1) & 1][2], b[(i >> 1) & 1][3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NT; i += 2) {
+            if (col_base + i * 8 < rank) {
+              uint32_t b[4];
+              ldsm_x4_trans(b, vb + i * 8);
+              mma_bf16(o[i], pa[ks], b[0], b[1]);
+              mma_bf16(o[i + 1], pa[ks], b[2], b[3]);
+            }
           }
         }
       }
@@ -365,8 +401,9 @@ extern "C" int cpi_latent_attention(const void* q, const void* cache, void* out,
                       + (size_t)lat::BM * lat::SLD * sizeof(float) + lat::BM * sizeof(int);
 #define CPI_LAT_LAUNCH(NT)                                                                                     \
   do {                                                                                                         \
-    cudaFuncSetAttribute(lat::latent_attention_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    cpi::launch_pdl(lat::latent_attention_kernel<NT>, grid, dim3(lat::THREADS), smem, stream, p);              \
+    auto kernel = rank == NT * 16 ? lat::latent_attention_kernel<NT, true> : lat::latent_attention_kernel<NT, false>; \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+    cpi::launch_pdl(kernel, grid, dim3(lat::THREADS), smem, stream, p);                                        \
   } while (0)
   if (rank <= 128) CPI_LAT_LAUNCH(8);
   else if (rank <= 256) CPI_LAT_LAUNCH(16);
