@@ -158,25 +158,16 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) 
       const __nv_bfloat16* kb = KV + (size_t)(ch * 16 + (lane >> 4) * 8 + (lane & 7)) * LD + ((lane >> 3) & 1) * 8;
       uint32_t a0[4], b0[4], a1[4], b1[4];
       const int pairs_end = row & ~31;
-      if (pairs_end > 0) {
-        ldsm_x4(a0, qa); ldsm_x4(b0, kb);
-        ldsm_x4(a1, qa + 16); ldsm_x4(b1, kb + 16);
-      }
-#pragma unroll 2
+      ldsm_x4(a0, qa); ldsm_x4(b0, kb);                            // row >= 16: the first k-step is always there
       for (int kk = 0; kk < pairs_end; kk += 32) {
-        uint32_t na0[4], nb0[4], na1[4], nb1[4];
-        const int nk = kk + 32 < pairs_end ? kk + 32 : kk;        // the last turn loads its own again (unused)
-        ldsm_x4(na0, qa + nk); ldsm_x4(nb0, kb + nk);
+        ldsm_x4(a1, qa + kk + 16); ldsm_x4(b1, kb + kk + 16);
         mma_bf16(s[0], a0, b0[0], b0[1]);
         mma_bf16(s[1], a0, b0[2], b0[3]);
-        ldsm_x4(na1, qa + nk + 16); ldsm_x4(nb1, kb + nk + 16);
+        if (kk + 32 < row) { ldsm_x4(a0, qa + kk + 32); ldsm_x4(b0, kb + kk + 32); }
         mma_bf16(s2[0], a1, b1[0], b1[1]);
         mma_bf16(s2[1], a1, b1[2], b1[3]);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) { a0[u] = na0[u]; b0[u] = nb0[u]; a1[u] = na1[u]; b1[u] = nb1[u]; }
       }
-      if (pairs_end < row) {                                       // an odd number of k-steps: the last one
-        ldsm_x4(a0, qa + pairs_end); ldsm_x4(b0, kb + pairs_end);
+      if (pairs_end < row) {                                       // an odd number of k-steps: the last one is loaded
         mma_bf16(s[0], a0, b0[0], b0[1]);
         mma_bf16(s[1], a0, b0[2], b0[3]);
       }
