@@ -15,6 +15,7 @@ from . import build as _build
 F32, BF16 = 0, 1
 MODE_STORE, MODE_ADD, MODE_SWIGLU, MODE_GEGLU = 0, 1, 2, 3      # GEGLU: the gated mode with a gelu (tanh form) gate
 MODE_CLAMPED_GLU = 4             # the gated mode with g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
+MODE_STORE_RELU2 = 5             # the storing mode with max(x, 0)^2 applied to the float32 accumulator
 GATED_MODES = (MODE_SWIGLU, MODE_GEGLU, MODE_CLAMPED_GLU)
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}

@@ -36,7 +36,7 @@ from ..csrc import lib as K
 from ..phases import active as phases_active, phase
 from ..weights.store import TensorReq
 from .base import FeedForward, register_feed_forward
-from .linear import MODE_ADD, MODE_CLAMPED_GLU, MODE_GEGLU, MODE_STORE, MODE_SWIGLU, project
+from .linear import MODE_ADD, MODE_CLAMPED_GLU, MODE_GEGLU, MODE_STORE, MODE_STORE_RELU2, MODE_SWIGLU, project
 
 
 def _stack(a, b):
@@ -135,10 +135,8 @@ class DenseMLP(FeedForward):
     def forward(self, h, residual, batch, add=True):
         T = h.shape[0]
         with phase("mlp"):
-            z = self.ws.get("mlp_up", (T, self.inter), torch.float32)
             a = self.ws.get("mlp_act", (T, self.inter), h.dtype)
-            project(h, self.w_up, z)
-            K.relu_squared(z, a)
+            project(h, self.w_up, a, MODE_STORE_RELU2)          # the activation in the product's epilogue
             project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE)
 
 

@@ -316,9 +316,11 @@ def test_gated_token_input_part_in_both_precisions(T, W, n, layer, dtype):
 
 
 @pytest.mark.parametrize("T,I,H,dtype", [(5, 44, 52, torch.float32), (40, 200, 136, torch.bfloat16),
-                                         (600, 256, 128, torch.bfloat16), (7, 96, 64, torch.bfloat16)])
+                                         (600, 256, 128, torch.bfloat16), (7, 96, 64, torch.bfloat16),
+                                         (8, 512, 4096, torch.bfloat16), (1, 1024, 2048, torch.bfloat16)])
 def test_squared_relu_feed_forward_part(T, I, H, dtype):
-    """down(max(up h, 0)^2) added to the residual, on the float32 pipe, the tensor-core kernel and the paired one."""
+    """down(max(up h, 0)^2) added to the residual, on the float32 pipe, the tensor-core kernel (also with the
+    contraction split over blocks: the activation acts on the whole sum) and the paired one."""
     from cpi_b200.config.spec import PartSpec
     from cpi_b200.parts.base import build_part
     from cpi_b200.parts.workspace import Workspace
