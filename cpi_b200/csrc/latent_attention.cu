@@ -26,7 +26,7 @@
 namespace cpi {
 namespace lat {
 
-constexpr int BM = 64, BN = 32, THREADS = 256, SLD = BN + 8;
+constexpr int BM_MAX = 64, BN = 32, SLD = BN + 8;      // a block has RG groups of 16 query rows (1, 2 or 4), 64 threads a group
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct Params {
@@ -68,8 +68,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int NT, bool FULL>
-__global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) {
+template <int NT, bool FULL, int RG>
+__global__ void __launch_bounds__(64 * RG, 1) latent_attention_kernel(Params p) {
+  constexpr int BM = 16 * RG, THREADS = 64 * RG;
   pdl_launch_dependents();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_wait();
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(THREADS, 1) latent_attention_kernel(Params p) 
   if (t_begin < t_end) load_kv(t_begin, 0);
   cp_async_commit();
 
-  const int rg = warp & 3, ch = warp >> 2;
+  const int rg = warp % RG, ch = warp / RG;
   const int g = lane >> 2, t4 = lane & 3;
   const bool active = rg * 16 < n_rows;
   float o[NT][4];
@@ -324,13 +325,20 @@ __global__ void __launch_bounds__(128) latent_combine_kernel(const float* part_o
   __syncthreads();
   const float inv = inv_s;
   __nv_bfloat16* dst = out + ((size_t)head * n_tokens + tok) * rank;
-  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
-    float acc = 0.f;
+  // four columns a thread (rank is a multiple of 16); every split's block has written its partial row (zeros when
+  // it had no keys), so the loads need no condition and eight of them are in flight
+  for (int c = threadIdx.x * 4; c < rank; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* src = part_o + slot0 * rank + c;
+#pragma unroll 8
     for (int s = 0; s < n_splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(src + (size_t)s * rank);
       const float w = w_s[s];
-      if (w > 0.f) acc = fmaf(w, part_o[(slot0 + s) * rank + c], acc);
+      acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y);
+      acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
     }
-    dst[c] = __float2bfloat16_rn(acc * inv);
+    *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    *reinterpret_cast<__nv_bfloat162*>(dst + c + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
   }
 }
 
@@ -346,6 +354,15 @@ extern "C" int cpi_latent_attention_supported(int row, int rank) {
 }
 
 extern "C" int cpi_latent_attention_max_splits() { return lat::kMaxSplits; }
+
+static int lat_row_groups(int n_heads, bool runs) {
+  const int most = n_heads < lat::BM_MAX ? n_heads : lat::BM_MAX;
+  return runs || most > 32 ? 4 : most > 16 ? 2 : 1;
+}
+static size_t lat_smem(int bm, int row) {
+  return (size_t)(bm + 2 * lat::BN) * (row + 8) * sizeof(__nv_bfloat16) + (size_t)bm * lat::SLD * sizeof(float)
+         + bm * sizeof(int);
+}
 
 // q [T, H, row] bfloat16; cache [pages, 1, page_size, row] bfloat16; out [H T, rank] bfloat16, head-major.
 // tile_tok0 / tile_rows (n_tiles of them, of at most max_tile_rows tokens): runs of consecutive tokens of one
@@ -376,8 +393,16 @@ extern "C" int cpi_latent_attention(const void* q, const void* cache, void* out,
   p.tile_tok0 = tile_tok0; p.tile_rows = tile_rows;
   p.sink = sink;
   p.n_tokens = n_tokens; p.n_heads = n_heads; p.row = row; p.rank = rank;
-  p.heads_per_group = n_heads < lat::BM ? n_heads : lat::BM;
-  p.tokens_per_block = lat::BM / p.heads_per_group;
+  // rows of a block: 64 in a prompt; for single tokens no more groups of 16 than the heads fill, so that the
+  // blocks are small, two share a multiprocessor and the keys can be divided further
+  // single tokens: small blocks (several to a multiprocessor) only when there are more blocks than multiprocessors;
+  // below that a block of eight warps is faster, its idle warps fetching the tiles
+  const int hg64 = (n_heads + lat::BM_MAX - 1) / lat::BM_MAX;
+  const bool crowded = tile_tok0 == nullptr && (long)n_tokens * n_splits * hg64 > sm_count();
+  const int rg = crowded ? lat_row_groups(n_heads, false) : 4;
+  const int bm = 16 * rg;
+  p.heads_per_group = n_heads < bm ? n_heads : bm;
+  p.tokens_per_block = bm / p.heads_per_group;
   p.n_splits = n_splits;
   p.scale_log2 = scale * lat::kLog2e;
   const int head_groups = (n_heads + p.heads_per_group - 1) / p.heads_per_group;
@@ -388,17 +413,24 @@ extern "C" int cpi_latent_attention(const void* q, const void* cache, void* out,
   } else {
     grid = dim3(n_tokens, n_splits, head_groups);
   }
-  const size_t smem = (size_t)(lat::BM + 2 * lat::BN) * (row + 8) * sizeof(__nv_bfloat16)
-                      + (size_t)lat::BM * lat::SLD * sizeof(float) + lat::BM * sizeof(int);
+  const size_t smem = lat_smem(bm, row);
+#define CPI_LAT_LAUNCH_RG(NT, RG)                                                                              \
+  do {                                                                                                         \
+    auto kernel = rank == NT * 16 ? lat::latent_attention_kernel<NT, true, RG>                                 \
+                                  : lat::latent_attention_kernel<NT, false, RG>;                               \
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
+    cpi::launch_pdl(kernel, grid, dim3(64 * RG), smem, stream, p);                                             \
+  } while (0)
 #define CPI_LAT_LAUNCH(NT)                                                                                     \
   do {                                                                                                         \
-    auto kernel = rank == NT * 16 ? lat::latent_attention_kernel<NT, true> : lat::latent_attention_kernel<NT, false>; \
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
-    cpi::launch_pdl(kernel, grid, dim3(lat::THREADS), smem, stream, p);                                        \
+    if (rg == 4) CPI_LAT_LAUNCH_RG(NT, 4);                                                                     \
+    else if (rg == 2) CPI_LAT_LAUNCH_RG(NT, 2);                                                                \
+    else CPI_LAT_LAUNCH_RG(NT, 1);                                                                             \
   } while (0)
   if (rank <= 128) CPI_LAT_LAUNCH(8);
   else if (rank <= 256) CPI_LAT_LAUNCH(16);
   else CPI_LAT_LAUNCH(32);
+#undef CPI_LAT_LAUNCH_RG
 #undef CPI_LAT_LAUNCH
   if (check_launch("latent_attention")) return 1;
   if (n_splits > 1) {

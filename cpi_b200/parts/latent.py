@@ -142,7 +142,7 @@ class LatentAttentionMixer(Mixer):
                     # key splits from a bucketed bound of the context, so that a captured graph keeps its shape
                     groups = -(-H // 64)
                     tiles = -(-batch.ctx_bucket // K.LATENT_KEY_TILE)
-                    n_splits = max(1, min(K.sm_count() // max(1, T * groups), tiles // 4,
+                    n_splits = max(1, min(K.sm_count() // max(1, T * groups), tiles // 2,
                                           K.latent_attention_max_splits()))
                     K.latent_attention(full, lat, pages, table, page_size, batch.token_seq, batch.token_pos,
                                        batch.seq_slot, n_heads=H, rank=rank, scale=self.scale, sink=self.sink,

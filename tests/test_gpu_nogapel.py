@@ -412,7 +412,7 @@ def test_a_far_row_and_the_sink_in_attention_over_shared_rows(row, heads, dtype)
 
 
 @pytest.mark.parametrize("H,row,rank", [(6, 128, 96), (16, 576, 512), (80, 48, 32), (5, 208, 192), (3, 16, 16),
-                                        (4, 160, 128), (2, 256, 256), (7, 80, 48)])
+                                        (4, 160, 128), (2, 256, 256), (7, 80, 48), (20, 64, 48), (40, 32, 16)])
 def test_tensor_core_attention_over_shared_rows_against_plain_softmax(H, row, rank):
     """The kernel that stacks the heads of a few tokens into one tile, against softmax in float64 over the same
     rounded rows: sequences that start at zero and in the middle, at page and key-tile borders, in scattered pages; one
