@@ -247,6 +247,11 @@ struct QkvPrepParams {
   float* v_first; long v_first_stride;   // value mixing (float32 [T, NKV DV]): v_mix_mode 1 stores this layer's values
   const void* v_mix; int v_mix_dtype;    // there; 2 writes v <- (1 - m) v + m v_first[t] with the one number m = *v_mix
   int v_mix_mode;
+  int maps;                              // 1, or 2: q rows hold 2 NH heads and k rows 2 NKV heads, the second halves being the
+  void* q2_out; void* k2_cache;          // heads of a second score map, which go to q2_out and k2_cache (shaped like the first)
+  int v_from_k;                          // the values are the k rows as projected (bias added, before any norm); rows hold no v
+  int temperature; float floor_scale; float attn_scale;      // q *= 1 + attn_scale * ln(floor((pos + 1) / floor_scale) + 1)
+  float rot_amp;                         // the sines and cosines of the rotation are multiplied by this
 };
 
 // which element a rotated element d is paired with, whether it is the pair's first, and the pair's frequency index
@@ -263,9 +268,10 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   pdl_wait();
   const int t = blockIdx.x, tid = threadIdx.x;
   const int D = p.head_dim, DV = p.v_dim;
-  const int nq = p.n_heads * D, nk = p.write_kv ? p.n_kv_heads * D : 0, nv = p.write_kv ? p.n_kv_heads * DV : 0;
+  const int nq = p.maps * p.n_heads * D, nk = p.write_kv ? p.maps * p.n_kv_heads * D : 0, nv = p.write_kv ? p.n_kv_heads * DV : 0;
   const TI* src = reinterpret_cast<const TI*>(p.qkv) + (size_t)t * p.qkv_stride;
   const int pos = p.token_pos[t];
+  const float temp = p.temperature ? 1.0f + p.attn_scale * logf(floorf(((float)pos + 1.0f) / p.floor_scale) + 1.0f) : 1.0f;
   float ssq = 0.f, ssk = 0.f;
   for (int i = tid; i < nq + nk; i += blockDim.x) {
     float x = to_f32(src[i]);
@@ -289,6 +295,17 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
     const int page = p.page_table[(size_t)slot * p.max_blocks + pos / p.page_size];
     kv_row = (size_t)page * p.n_kv_heads * p.page_size + pos % p.page_size;      // row of kv head 0
   }
+  // element i of the q part / element e of the k part, to the first map's buffer or the second's
+  auto store_q = [&](int i, float x) {
+    const int hd = i / D;
+    TO* base = reinterpret_cast<TO*>(hd < p.n_heads ? p.q_out : p.q2_out);
+    base[((size_t)t * p.n_heads + hd % p.n_heads) * D + i % D] = from_f32<TO>(x * temp);
+  };
+  auto store_k = [&](int e, float x) {
+    const int hd = e / D;
+    TO* base = reinterpret_cast<TO*>(hd < p.n_kv_heads ? p.k_cache : p.k2_cache);
+    base[(kv_row + (size_t)(hd % p.n_kv_heads) * p.page_size) * D + e % D] = from_f32<TO>(x);
+  };
   const int half = p.rot_dims >> 1;
   float* rot_s = row_s + nq + nk;                        // head_norm: the rotated row, then one factor per head
   float* inv_s = rot_s + nq + nk;
@@ -302,6 +319,7 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
         const float other = row_s[i - d + od];
         float sn, cs;
         sincosf((float)pos * p.inv_freq[f], &sn, &cs);
+        sn *= p.rot_amp; cs *= p.rot_amp;
         x = first ? x * cs - other * sn : x * cs + other * sn;
       }
       rot_s[i] = x;
@@ -319,8 +337,8 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
       const bool is_q = i < nq;
       const int e = is_q ? i : i - nq;
       const float x = rot_s[i] * inv_s[i / D];
-      if (is_q) reinterpret_cast<TO*>(p.q_out)[(size_t)t * nq + i] = from_f32<TO>(x);
-      else reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)(e / D) * p.page_size) * D + e % D] = from_f32<TO>(x);
+      if (is_q) store_q(i, x);
+      else store_k(e, x);
     }
   }
   if (p.head_norm == 2) {
@@ -352,10 +370,11 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
         const float other = normed(i - d + od, od);
         float sn, cs;
         sincosf((float)pos * p.inv_freq[f], &sn, &cs);
+        sn *= p.rot_amp; cs *= p.rot_amp;
         x = first ? x * cs - other * sn : x * cs + other * sn;
       }
-      if (is_q) reinterpret_cast<TO*>(p.q_out)[(size_t)t * nq + i] = from_f32<TO>(x);
-      else reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)hd * p.page_size) * D + d] = from_f32<TO>(x);
+      if (is_q) store_q(i, x);
+      else store_k(e, x);
     }
   }
   for (int i = tid; i < (p.head_norm ? 0 : nq + nk); i += blockDim.x) {
@@ -376,17 +395,20 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
       const float other = normed(i - d + od, e - d + od);
       float sn, cs;
       sincosf((float)pos * p.inv_freq[f], &sn, &cs);
+      sn *= p.rot_amp; cs *= p.rot_amp;
       x = first ? x * cs - other * sn : x * cs + other * sn;
     }
-    if (is_q) {
-      reinterpret_cast<TO*>(p.q_out)[(size_t)t * nq + i] = from_f32<TO>(x);
-    } else {
-      reinterpret_cast<TO*>(p.k_cache)[(kv_row + (size_t)hd * p.page_size) * D + d] = from_f32<TO>(x);
-    }
+    if (is_q) store_q(i, x);
+    else store_k(e, x);
   }
   for (int i = tid; i < nv; i += blockDim.x) {
-    float x = to_f32(src[nq + nk + i]);
-    if (p.bias) x += load_any(p.bias, p.bias_dtype, nq + nk + i);
+    float x;
+    if (p.v_from_k) {
+      x = row_s[nq + i];                                 // the key as projected, its bias added, before the norm
+    } else {
+      x = to_f32(src[nq + nk + i]);
+      if (p.bias) x += load_any(p.bias, p.bias_dtype, nq + nk + i);
+    }
     if (p.v_mix_mode == 1) {
       p.v_first[(size_t)t * p.v_first_stride + i] = x;
     } else if (p.v_mix_mode == 2) {
@@ -409,6 +431,7 @@ struct AttnParams {
   const float* sink;                     // [NH] float32 or null: exp(sink[h]) joins the softmax denominator (no key, no value)
   int v_dim;                             // elements of a value row (the cache's v stream); keys have head_dim
   int keep_first;                        // a sequence's first positions that stay visible below a sliding window
+  float softcap;                         // > 0: score <- softcap * tanh(score / softcap) after the scale
 };
 
 __device__ __forceinline__ int window_low(int kind, int size, int pos) {
@@ -463,6 +486,7 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(q_s[d], to_f32(kr[d]), dot);
       s = dot * p.scale;
+      if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
       if (p.score_bias) s += p.score_bias[(size_t)h * p.n_dist + min(pos - kp, p.n_dist - 1)];
     }
     const float m_new = fmaxf(m_run, block_max(s, scratch));
@@ -491,9 +515,64 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
     if (tid + a * ATT_NT < DV) o[tid + a * ATT_NT] = from_f32<T>(acc[a] * inv);
 }
 
+// What follows attention, per token and head, before the output projection (one warp a head):
+//   o = a1 - lambda * a2        (a2: the output of a second score map over the same values; null: o = a1)
+//   o <- o / sqrt(mean(o^2) + eps) * norm_scale      (when `norm`: over the head's values, no weight)
+//   o <- o * sigmoid(gate[t, h])                     (when `gate`: one number per token and head, float32 before its sigmoid)
+// in float32, rounded once into `out` (which may be a1).
+struct HeadPostParams {
+  const void* a1; const void* a2; void* out;             // [T, NH * DV]
+  float lambda; int norm; float eps; float norm_scale;
+  const float* gate; long gate_stride;
+  int n_tokens, n_heads, v_dim;
+};
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128) head_post_kernel(HeadPostParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long r = (long)blockIdx.x * (blockDim.x >> 5) + warp;           // (token, head)
+  if (r >= (long)p.n_tokens * p.n_heads) return;
+  const int t = (int)(r / p.n_heads), h = (int)(r % p.n_heads);
+  const int DV = p.v_dim;
+  const TI* a1 = reinterpret_cast<const TI*>(p.a1) + (size_t)r * DV;
+  const TI* a2 = p.a2 ? reinterpret_cast<const TI*>(p.a2) + (size_t)r * DV : nullptr;
+  TO* o = reinterpret_cast<TO*>(p.out) + (size_t)r * DV;
+  float f = 1.0f;
+  if (p.norm) {
+    float ss = 0.f;
+    for (int d = lane; d < DV; d += 32) {
+      const float x = a2 ? to_f32(a1[d]) - p.lambda * to_f32(a2[d]) : to_f32(a1[d]);
+      ss = fmaf(x, x, ss);
+    }
+    f = p.norm_scale / sqrtf(warp_sum(ss) / (float)DV + p.eps);
+  }
+  if (p.gate) f *= 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.gate_stride + h]));
+  for (int d = lane; d < DV; d += 32) {
+    const float x = a2 ? to_f32(a1[d]) - p.lambda * to_f32(a2[d]) : to_f32(a1[d]);
+    o[d] = from_f32<TO>(x * f);
+  }
+}
+
 }  // namespace cpi
 
 using namespace cpi;
+
+extern "C" int cpi_head_post(const void* a1, const void* a2, int in_dtype, void* out, int out_dtype, float lambda,
+                             int norm, float eps, float norm_scale, const float* gate, long gate_stride, int n_tokens,
+                             int n_heads, int v_dim, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(n_heads > 0 && v_dim > 0, "head_post: %d heads of %d values", n_heads, v_dim);
+  HeadPostParams p{a1, a2, out, lambda, norm, eps, norm_scale, gate, gate_stride, n_tokens, n_heads, v_dim};
+  const long rows = (long)n_tokens * n_heads;
+  const dim3 grid((unsigned)((rows + 3) / 4));
+  if (in_dtype == kF32 && out_dtype == kF32) cpi::launch_pdl(head_post_kernel<float, float>, grid, 128, 0, stream, p);
+  else if (in_dtype == kF32 && out_dtype == kBF16) cpi::launch_pdl(head_post_kernel<float, __nv_bfloat16>, grid, 128, 0, stream, p);
+  else if (in_dtype == kBF16 && out_dtype == kBF16) cpi::launch_pdl(head_post_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 128, 0, stream, p);
+  else { set_error("head_post: input dtype %d with output dtype %d is not supported", in_dtype, out_dtype); return 1; }
+  return check_launch("head_post");
+}
 
 static int check_head(const char* who, int n_heads, int n_kv_heads, int head_dim) {
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
@@ -542,7 +621,9 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
                                const int* token_seq, const int* token_pos, const int* seq_slot, int n_tokens,
                                int n_heads, int n_kv_heads, int head_dim, int v_dim, int write_kv, int head_norm,
                                int interleaved, float* v_first, long v_first_stride, const void* v_mix,
-                               int v_mix_dtype, int v_mix_mode, cudaStream_t stream) {
+                               int v_mix_dtype, int v_mix_mode, int maps, void* q2_out, void* k2_cache, int v_from_k,
+                               int temperature, float floor_scale, float attn_scale, float rot_amp,
+                               cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
               "qkv_prepare: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
@@ -552,14 +633,20 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
   QkvPrepParams p{qkv, qkv_stride, bias, bias_dtype, q_norm, k_norm, norm_dtype, norm_whole, norm_eps, inv_freq,
                   rot_dims, q_out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos,
                   seq_slot, n_heads, n_kv_heads, head_dim, v_dim, write_kv, head_norm, interleaved, v_first,
-                  v_first_stride, v_mix, v_mix_dtype, v_mix_mode};
+                  v_first_stride, v_mix, v_mix_dtype, v_mix_mode, maps, q2_out, k2_cache, v_from_k, temperature,
+                  floor_scale, attn_scale, rot_amp};
+  CPI_REQUIRE(maps == 1 || (maps == 2 && q2_out != nullptr && (!write_kv || k2_cache != nullptr)),
+              "qkv_prepare: one score map, or two with buffers for the second map's queries and keys");
+  CPI_REQUIRE(!v_from_k || (maps == 1 && v_dim == head_dim && v_mix_mode == 0),
+              "qkv_prepare: values that are the projected keys have the keys' size, one map and no value mixing");
+  CPI_REQUIRE(!temperature || floor_scale > 0.f, "qkv_prepare: a query temperature needs a positive period");
   CPI_REQUIRE(!(head_norm && norm_whole), "qkv_prepare: a norm over the whole projection or one per head, not both");
   CPI_REQUIRE(head_norm >= 0 && head_norm <= 2, "qkv_prepare: unknown kind of head norm %d", head_norm);
   CPI_REQUIRE(v_mix_mode == 0 || (v_first != nullptr && write_kv && (v_mix_mode == 1 || (v_mix_mode == 2 && v_mix))),
               "qkv_prepare: value mixing needs the buffer of the first values (and, to mix, the mixing weight)");
-  const size_t row = (size_t)(n_heads + (write_kv ? n_kv_heads : 0)) * head_dim;
-  const size_t smem = (head_norm == 1 ? 2 * row + n_heads + n_kv_heads : head_norm == 2 ? row + n_heads + n_kv_heads : row)
-                      * sizeof(float);
+  const size_t row = (size_t)maps * (n_heads + (write_kv ? n_kv_heads : 0)) * head_dim;
+  const size_t n_norms = (size_t)maps * (n_heads + n_kv_heads);
+  const size_t smem = (head_norm == 1 ? 2 * row + n_norms : head_norm == 2 ? row + n_norms : row) * sizeof(float);
   CPI_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a q and k row of %zu bytes does not fit in shared memory", smem);
   // with few tokens the blocks are large (a few elements per thread); a prompt has blocks enough
   const int threads = n_tokens <= 2 * sm_count() ? 1024 : 256;
@@ -582,7 +669,8 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
                                      const int* token_seq, const int* token_pos, const int* seq_slot,
                                      int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                      int window_kind, int window_size, float scale, const float* score_bias,
-                                     int n_dist, const float* sink, int v_dim, int keep_first, cudaStream_t stream) {
+                                     int n_dist, const float* sink, int v_dim, int keep_first, float softcap,
+                                     cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
               "attention: %d heads cannot be grouped over %d key/value heads", n_heads, n_kv_heads);
@@ -593,7 +681,7 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
   CPI_REQUIRE(n_heads <= 65535, "attention: too many heads (%d)", n_heads);
   AttnParams p{q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos, seq_slot,
                n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias, n_dist, sink, v_dim,
-               window_kind == 2 && keep_first > 0 ? keep_first : 0};
+               window_kind == 2 && keep_first > 0 ? keep_first : 0, softcap};
   dim3 grid(n_tokens, n_heads);
   CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(attention_general_kernel<T>, grid, ATT_NT, 0, stream, p));
   return check_launch("attention_general");

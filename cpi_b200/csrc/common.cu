@@ -46,4 +46,4 @@ extern "C" int cpi_sm_count() { return cpi::sm_count(); }
 extern "C" const char* cpi_last_error() { return cpi::g_error; }
 
 // The calling convention of this library's entry points; the loader refuses a library that answers another number.
-extern "C" int cpi_abi_version() { return 4; }
+extern "C" int cpi_abi_version() { return 5; }

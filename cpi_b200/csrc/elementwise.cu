@@ -262,6 +262,60 @@ __global__ void __launch_bounds__(256) branch_norm_sum_kernel(BranchSumParams p)
   }
 }
 
+// A sublayer's output enters the residual through a norm of its own:
+//   out[t] (+)= rmsnorm(sum_b scale_b * y_b[t]) * w,     and optionally   h_out[t] = out[t] in another dtype
+// (the sublayer's output may be several branches with a constant each; h_out is the next sublayer's input when the
+// sublayers read the residual itself).  One block per token, float32 throughout.
+struct SumNormAddParams {
+  const float* y[kMaxBranches]; long y_stride[kMaxBranches]; float scale[kMaxBranches];
+  const void* w; int w_dtype; int n_branches, width, add; float eps;
+  float* out; long out_stride;
+  void* h_out; long h_stride;
+  int normalise;                         // 0: the scaled sum enters as it is
+};
+
+template <typename TH>
+__global__ void __launch_bounds__(256) sum_norm_add_kernel(SumNormAddParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  auto branches = [&](int i) {
+    float v = 0.f;
+#pragma unroll
+    for (int b = 0; b < kMaxBranches; ++b)
+      if (b < p.n_branches) v = fmaf(p.scale[b], p.y[b][(size_t)t * p.y_stride[b] + i], v);
+    return v;
+  };
+  float inv = 1.0f;
+  if (p.normalise) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < p.width; i += blockDim.x) { const float v = branches(i); ss = fmaf(v, v, ss); }
+    inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)p.width + p.eps);
+  }
+  float* o = p.out + (size_t)t * p.out_stride;
+  TH* h = p.h_out ? reinterpret_cast<TH*>(p.h_out) + (size_t)t * p.h_stride : nullptr;
+  for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
+    float v = branches(i) * inv;
+    if (p.w) v *= load_any(p.w, p.w_dtype, i);
+    if (p.add) v += o[i];
+    o[i] = v;
+    if (h) h[i] = from_f32<TH>(v);
+  }
+}
+
+// out[t, :] (+)= bias: float32 rows that a product then adds into, so that the product carries a bias
+__global__ void __launch_bounds__(256) bias_rows_kernel(float* __restrict__ out, long out_stride, const void* bias,
+                                                        int bias_dtype, int width, int add) {
+  pdl_launch_dependents();
+  pdl_wait();
+  float* o = out + (size_t)blockIdx.x * out_stride;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float b = load_any(bias, bias_dtype, i);
+    o[i] = add ? o[i] + b : b;
+  }
+}
+
 // out[t] = [a[t] | b[t]] in out's dtype: two float32 rows side by side as one operand row of a product
 template <typename TO>
 __global__ void __launch_bounds__(256) concat_rows_kernel(const float* __restrict__ a, const float* __restrict__ b,
@@ -393,6 +447,27 @@ extern "C" int cpi_branch_norm_sum(const float* const* y, const long* y_stride, 
   p.out = out; p.out_stride = out_stride;
   cpi::launch_pdl(branch_norm_sum_kernel, n_rows, 256, 0, stream, p);
   return check_launch("branch_norm_sum");
+}
+
+extern "C" int cpi_sum_norm_add(const float* const* y, const long* y_stride, const float* scale, int n_branches,
+                                const void* w, int w_dtype, int n_rows, int width, float eps, int add, float* out,
+                                long out_stride, void* h_out, int h_dtype, long h_stride, int normalise,
+                                cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_REQUIRE(n_branches >= 1 && n_branches <= kMaxBranches, "sum_norm_add: %d branches (1 to %d)", n_branches, kMaxBranches);
+  SumNormAddParams p{};
+  for (int b = 0; b < n_branches; ++b) { p.y[b] = y[b]; p.y_stride[b] = y_stride[b]; p.scale[b] = scale[b]; }
+  p.w = w; p.w_dtype = w_dtype; p.n_branches = n_branches; p.width = width; p.add = add; p.eps = eps;
+  p.out = out; p.out_stride = out_stride; p.h_out = h_out; p.h_stride = h_stride; p.normalise = normalise;
+  CPI_DISPATCH_DTYPE(h_dtype, TH, cpi::launch_pdl(sum_norm_add_kernel<TH>, n_rows, 256, 0, stream, p));
+  return check_launch("sum_norm_add");
+}
+
+extern "C" int cpi_bias_rows(float* out, long out_stride, const void* bias, int bias_dtype, int n_rows, int width,
+                             int add, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  cpi::launch_pdl(bias_rows_kernel, n_rows, 256, 0, stream, out, out_stride, bias, bias_dtype, width, add);
+  return check_launch("bias_rows");
 }
 
 extern "C" int cpi_concat_rows(const float* a, const float* b, void* out, int out_dtype, int n_rows, int wa, int wb,

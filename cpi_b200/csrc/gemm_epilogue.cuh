@@ -37,9 +37,11 @@ __device__ __forceinline__ float gate_mul(float g, float u, int act, float limit
   return __fdividef(g, 1.0f + __expf(-inner)) * u;
 }
 
-// The stored value of a product without a gate may pass an activation: 3 the square of relu, max(x, 0)^2.
+// The stored value of a product without a gate may pass an activation: 3 the square of relu, max(x, 0)^2;
+// 4 the tanh form of gelu, x * sigmoid(2 c (x + 0.044715 x^3)) as in gate_mul.
 __device__ __forceinline__ float store_act(float x, int act) {
   if (act == 3) { x = fmaxf(x, 0.f); x *= x; }
+  if (act == 4) x = __fdividef(x, 1.0f + __expf(-1.5957691216057308f * fmaf(0.044715f * x * x, x, x)));
   return x;
 }
 

@@ -141,6 +141,7 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(GemmParams p) {
         o[n] = from_f32<TO>(to_f32(o[n]) + v);
       } else {
         if (p.gate_act == 3) { v = fmaxf(v, 0.f); v *= v; }      // the storing mode with a squared relu
+        if (p.gate_act == 4) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));   // ... a gelu
         o[n] = from_f32<TO>(v);
       }
     }
@@ -185,10 +186,10 @@ extern "C" int cpi_gemm_simt(const void* a, int a_dtype, long lda, const int* a_
                              int M, int N, int K, int mode, int rows_per_group_hint, float gate_limit,
                              cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  // modes 3, 4: the gated mode with a gelu / a clamped gate; mode 5: the storing mode with a squared relu
-  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : mode == 5 ? 3 : 0;
+  // modes 3, 4: the gated mode with a gelu / a clamped gate; modes 5, 6: the storing mode with a squared relu / a gelu
+  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : mode == 5 ? 3 : mode == 6 ? 4 : 0;
   if (mode == 3 || mode == 4) mode = 2;
-  if (mode == 5) mode = 0;
+  if (mode == 5 || mode == 6) mode = 0;
   CPI_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
   CPI_REQUIRE(mode != kAdd || out_dtype == kF32, "gemm: ADD mode needs a float32 output");
   GemmParams p{a, lda, a_rows, w, ldw, w_group_stride, out, ldo, out_rows, row_scale,

@@ -699,10 +699,10 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
                            int T, int N, int K, int mode, int bn, int splits, int* error_flag, float gate_limit,
                            cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
-  // modes 3, 4: the gated mode with a gelu / a clamped gate; mode 5: the storing mode with a squared relu
-  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : mode == 5 ? 3 : 0;
+  // modes 3, 4: the gated mode with a gelu / a clamped gate; modes 5, 6: the storing mode with a squared relu / a gelu
+  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : mode == 5 ? 3 : mode == 6 ? 4 : 0;
   if (mode == 3 || mode == 4) mode = 2;
-  if (mode == 5) mode = 0;
+  if (mode == 5 || mode == 6) mode = 0;
   CPI_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
   CPI_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K (%d) and the activation row stride (%ld) must be multiples of 8", K, ldx);
   CPI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,

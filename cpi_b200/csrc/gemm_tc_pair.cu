@@ -662,10 +662,10 @@ extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* ou
                                 int T, int N, int K, int mode, int bn, int* error_flag, float gate_limit,
                                 cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
-  // modes 3, 4: the gated mode with a gelu / a clamped gate; mode 5: the storing mode with a squared relu
-  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : mode == 5 ? 3 : 0;
+  // modes 3, 4: the gated mode with a gelu / a clamped gate; modes 5, 6: the storing mode with a squared relu / a gelu
+  const int gate_act = mode == 3 ? 1 : mode == 4 ? 2 : mode == 5 ? 3 : mode == 6 ? 4 : 0;
   if (mode == 3 || mode == 4) mode = 2;
-  if (mode == 5) mode = 0;
+  if (mode == 5 || mode == 6) mode = 0;
   CPI_REQUIRE(N % 256 == 0 && K % 8 == 0 && ldx % 8 == 0, "gemm_tc_pair: N (%d) must be a multiple of 256, K (%d) and the row stride of 8", N, K);
   CPI_REQUIRE(bn >= 32 && bn <= 256 && bn % 32 == 0, "gemm_tc_pair: token tile %d (multiples of 32 up to 256)", bn);
   CPI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, "gemm_tc_pair: operands must be 16-byte aligned");

@@ -16,6 +16,7 @@ F32, BF16 = 0, 1
 MODE_STORE, MODE_ADD, MODE_SWIGLU, MODE_GEGLU = 0, 1, 2, 3      # GEGLU: the gated mode with a gelu (tanh form) gate
 MODE_CLAMPED_GLU = 4             # the gated mode with g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1)
 MODE_STORE_RELU2 = 5             # the storing mode with max(x, 0)^2 applied to the float32 accumulator
+MODE_STORE_GELU = 6              # the storing mode with the tanh form of gelu applied to the float32 accumulator
 GATED_MODES = (MODE_SWIGLU, MODE_GEGLU, MODE_CLAMPED_GLU)
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
@@ -23,7 +24,7 @@ MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode 
 GENERAL_ATTENTION_MAX_DIM = 640  # largest key or value row of the general attention kernel
 PREFILL_TILE_ROWS = 256          # most query rows of one sequence that a block of the prefill attention kernel takes
 
-ABI_VERSION = 4                  # what cpi_abi_version() of a matching library answers
+ABI_VERSION = 5                  # what cpi_abi_version() of a matching library answers
 
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
@@ -327,12 +328,13 @@ def qkv_post(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, tok
 
 def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
                       n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias=None, sink=None,
-                      value_dim=None, keep_first=0):
+                      value_dim=None, keep_first=0, softcap=0.0):
     """Attention of any head size and dtype over the paged cache.  `score_bias`: float32 [heads, n_dist] added
     to the scaled scores, indexed by the distance query position - key position (the last column for longer).
     `sink`: float32 [heads]; exp(sink[h]) is one more term of the softmax denominator, without a key or a value.
     `value_dim`: elements of a value row when it differs from the keys' `head_dim`.  `keep_first`: with a sliding
-    window, a sequence's first positions that every later query still sees."""
+    window, a sequence's first positions that every later query still sees.  `softcap` c > 0: a scaled score s
+    becomes c * tanh(s / c) before anything is added to it."""
     _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, score_bias, sink)
     assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype == v_cache.dtype
     assert score_bias is None or (score_bias.dtype == torch.float32 and score_bias.is_contiguous()
@@ -346,13 +348,14 @@ def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq
           _p(seq_slot), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind),
           c_int(window_size), c_float(scale), _p(score_bias),
           c_int(0 if score_bias is None else score_bias.shape[1]), _p(sink), c_int(value_dim), c_int(int(keep_first)),
-          _stream())
+          c_float(float(softcap or 0.0)), _stream())
 
 
 def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *, n_heads,
                 n_kv_heads, head_dim, value_dim, bias=None, q_norm=None, k_norm=None, norm_whole=False, norm_eps=0.0,
                 inv_freq=None, rotary_dims=0, write_kv=True, head_norm=False, interleaved=False, v_first=None,
-                v_mix=None, v_mix_mode=0):
+                v_mix=None, v_mix_mode=0, q2_out=None, k2_cache=None, values_from_keys=False, temperature=None,
+                rotary_amplitude=1.0):
     """The general form of `qkv_post`, a block per token: rows [q | k | v] (float32 or the cache's dtype) get
     their bias, q and k an RMS norm over the whole projection (`norm_whole`, weights `q_norm` / `k_norm`), the
     first `rotary_dims` elements of each head their rotation, and then (`head_norm` True or 1) every q and k head a
@@ -360,8 +363,18 @@ def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, 
     head is normed before the rotation and multiplied by `q_norm` / `k_norm` ([head_dim], shared by the heads).
     `interleaved`: the rotation pairs elements (2i, 2i + 1) instead of (i, i + rotary_dims / 2).  Value mixing:
     `v_mix_mode` 1 also stores the values (float32) in `v_first` [T, kv heads * value_dim]; 2 writes
-    (1 - m) v + m v_first[t] into the cache, m the one number `v_mix` holds."""
-    _need_cuda(qkv, q_out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, bias, q_norm, k_norm, inv_freq)
+    (1 - m) v + m v_first[t] into the cache, m the one number `v_mix` holds.  With `q2_out` (and `k2_cache`) the rows
+    hold two score maps: 2 * n_heads query heads and 2 * n_kv_heads key heads, the first halves going to q_out and
+    k_cache, the second halves to q2_out and k2_cache (shaped alike); values have n_kv_heads heads.
+    `values_from_keys`: rows are [q | k] and the cached values are the k rows as projected (bias added, before any
+    norm).  `temperature` (f, a): q *= 1 + a * ln(floor((position + 1) / f) + 1).  `rotary_amplitude` multiplies the
+    rotation's sines and cosines."""
+    _need_cuda(qkv, q_out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, bias, q_norm, k_norm, inv_freq,
+               q2_out, k2_cache)
+    maps = 1 if q2_out is None else 2
+    assert q2_out is None or (q2_out.is_contiguous() and q2_out.shape == q_out.shape and q2_out.dtype == q_out.dtype)
+    assert k2_cache is None or (k2_cache.shape == k_cache.shape and k2_cache.dtype == k_cache.dtype)
+    fl, sc = (temperature if temperature is not None else (1.0, 0.0))
     _rowmajor(qkv, "qkv_prepare qkv")
     T = qkv.shape[0]
     assert q_out.is_contiguous() and q_out.shape[1] == n_heads * head_dim
@@ -382,7 +395,87 @@ def qkv_prepare(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, 
           _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot),
           c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(value_dim), c_int(int(write_kv)),
           c_int(int(head_norm)), c_int(int(interleaved)), _p(v_first), c_long(0 if v_first is None else v_first.stride(0)),
-          _p(v_mix), c_int(F32 if v_mix is None else dtype_code(v_mix.dtype)), c_int(int(v_mix_mode)), _stream())
+          _p(v_mix), c_int(F32 if v_mix is None else dtype_code(v_mix.dtype)), c_int(int(v_mix_mode)), c_int(maps),
+          _p(q2_out), _p(k2_cache), c_int(int(values_from_keys)), c_int(int(temperature is not None)), c_float(fl),
+          c_float(sc), c_float(float(rotary_amplitude)), _stream())
+
+
+def head_post(a1, out, *, n_heads, value_dim, a2=None, lam=0.0, norm_eps=None, norm_scale=1.0, gate=None):
+    """What follows attention per token and head, before the output projection: o = a1 - lam * a2 (a2 None: a1), then
+    (norm_eps given) o / sqrt(mean(o^2) + norm_eps) * norm_scale over the head's values, then (gate given: float32
+    [T, >= heads] rows, a column slice allowed) o * sigmoid(gate[t, head]); float32 arithmetic, out may be a1."""
+    _need_cuda(a1, a2, out, gate)
+    T = a1.shape[0]
+    assert a1.is_contiguous() and out.is_contiguous() and a1.shape == out.shape == (T, n_heads * value_dim)
+    assert a2 is None or (a2.is_contiguous() and a2.shape == a1.shape and a2.dtype == a1.dtype)
+    assert gate is None or (gate.dtype == torch.float32 and gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[1] >= n_heads)
+    _call("cpi_head_post", _p(a1), _p(a2), c_int(dtype_code(a1.dtype)), _p(out), c_int(dtype_code(out.dtype)),
+          c_float(float(lam)), c_int(int(norm_eps is not None)), c_float(float(norm_eps or 0.0)), c_float(float(norm_scale)),
+          _p(gate), c_long(0 if gate is None else gate.stride(0)), c_int(T), c_int(n_heads), c_int(value_dim), _stream())
+
+
+def sum_norm_add(branches, scales, weight, out, *, eps=0.0, add=True, h_out=None, normalise=True):
+    """out (+)= rmsnorm(sum_b scales[b] * branches[b]) * weight over rows: up to four float32 [T, W] branches with a
+    constant each, one norm over their sum (`normalise` False: the scaled sum as it is); `h_out` (any dtype, [T, W])
+    also receives the new out rows."""
+    _need_cuda(out, weight, h_out, *branches)
+    n = len(branches)
+    T, W = out.shape
+    assert 1 <= n <= 4 and len(scales) == n and out.dtype == torch.float32 and out.stride(1) == 1
+    for y in branches:
+        assert y.dtype == torch.float32 and y.shape == (T, W) and y.stride(1) == 1
+    assert weight is None or (weight.is_contiguous() and weight.numel() == W)
+    assert h_out is None or (h_out.shape == (T, W) and h_out.stride(1) == 1)
+    ys = (c_void_p * n)(*[y.data_ptr() for y in branches])
+    st = (c_long * n)(*[y.stride(0) for y in branches])
+    sc = (c_float * n)(*[float(x) for x in scales])
+    _call("cpi_sum_norm_add", ys, st, sc, c_int(n), _p(weight), c_int(F32 if weight is None else dtype_code(weight.dtype)),
+          c_int(T), c_int(W), c_float(eps), c_int(int(add)), _p(out), c_long(out.stride(0)), _p(h_out),
+          c_int(F32 if h_out is None else dtype_code(h_out.dtype)), c_long(0 if h_out is None else h_out.stride(0)),
+          c_int(int(normalise)), _stream())
+
+
+def bias_rows(out, bias, *, add=False):
+    """out[t, :] (+)= bias for float32 rows out [T, W] (a row stride allowed), bias [W]."""
+    _need_cuda(out, bias)
+    assert out.dtype == torch.float32 and out.dim() == 2 and out.stride(1) == 1 and bias.is_contiguous()
+    assert bias.numel() == out.shape[1]
+    _call("cpi_bias_rows", _p(out), c_long(out.stride(0)), _p(bias), c_int(dtype_code(bias.dtype)), c_int(out.shape[0]),
+          c_int(out.shape[1]), c_int(int(add)), _stream())
+
+
+def block_major_rows(x, out, offsets, *, parts):
+    """out[b * T + t] = x[t, b * n : (b + 1) * n] in out's dtype, for float32 rows x [T, parts * n] (a column slice
+    allowed) and out [parts * T, n] contiguous; offsets (int32 [parts + 1]) receives b * T, the groups of a grouped
+    product with one group per part."""
+    _need_cuda(x, out, offsets)
+    T, W = x.shape
+    n = W // parts
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and W == parts * n and out.is_contiguous()
+    assert out.numel() == T * W and offsets.dtype == torch.int32 and offsets.numel() >= parts + 1
+    _call("cpi_block_major_rows", _p(x), c_long(x.stride(0)), _p(out), c_int(dtype_code(out.dtype)), _p(offsets),
+          c_int(T), c_int(parts), c_int(n), _stream())
+
+
+def rglru_scan(gates, u, y, state, out, batch, *, block, lam, r_bias=None, i_bias=None, y_bias=None, rate=8.0):
+    """The gated linear recurrent unit, a state per channel (float32 [slots, W], updated in place), per sequence:
+    r = sigmoid(g_r + r_bias), i = sigmoid(g_i + i_bias), log a = -rate * softplus(lam) * r,
+    S <- a S + sqrt(1 - a^2) * i * u, out = S * gelu_tanh(y + y_bias).  `gates`: float32 [W / block * T, 2 * block], row
+    b * T + t holding block b's two gate products of token t (g_r, then g_i); u, y: float32 [T, W] rows (column slices
+    allowed); the small vectors [W] of one dtype."""
+    small = [t for t in (lam, r_bias, i_bias, y_bias) if t is not None]
+    _need_cuda(gates, u, y, state, out, *small)
+    T, W = u.shape
+    assert W % block == 0 and gates.dtype == torch.float32 and gates.stride(1) == 1 and gates.shape == (W // block * T, 2 * block)
+    for t in (u, y):
+        assert t.dtype == torch.float32 and t.dim() == 2 and t.stride(1) == 1 and t.shape == (T, W)
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (W,)
+    assert out.shape == (T, W) and out.stride(1) == 1
+    assert all(t.dtype == lam.dtype and t.is_contiguous() and t.numel() == W for t in small)
+    _call("cpi_rglru_scan", _p(gates), c_long(gates.stride(0)), _p(r_bias), _p(i_bias), _p(lam), _p(y_bias),
+          c_int(dtype_code(lam.dtype)), _p(u), c_long(u.stride(0)), _p(y), c_long(y.stride(0)), _p(state), _p(out),
+          c_int(dtype_code(out.dtype)), c_long(out.stride(0)), _p(batch.seq_slot), _p(batch.seq_tok0), _p(batch.seq_new),
+          c_int(batch.n_seqs), c_int(batch.max_new), c_int(T), c_int(W), c_int(int(block)), c_float(float(rate)), _stream())
 
 
 def latent_kv_write(x, norm_weight, eps, inv_freq, interleaved, cache, page_table, page_size, token_seq, token_pos,
@@ -495,11 +588,13 @@ def hc_step(x, *, y=None, mix=None, write=None, read=None, rows=None, norm_weigh
           c_long(0 if h_out is None else h_out.stride(0)), _p(sum_out), _stream())
 
 
-def causal_conv(x, weight, bias, carry, out, batch, *, silu=True):
+def causal_conv(x, weight, bias, carry, out, batch, *, silu=True, in_bias=None):
     """out[t, c] = act(bias[c] + sum_j weight[c, j] x[t - (taps - 1) + j, c]) per sequence of the step; inputs
     before the step's first token come from carry[slot] ([slots, taps - 1, C] float32), which afterwards holds the
-    sequence's last taps - 1 inputs.  x, out: float32 [T, C] (x may be a column slice)."""
-    _need_cuda(x, weight, bias, carry, out)
+    sequence's last taps - 1 inputs.  x, out: float32 [T, C] (x may be a column slice).  `in_bias` [C] (the weight's
+    dtype) is added to every input of the step before it is used or carried."""
+    _need_cuda(x, weight, bias, carry, out, in_bias)
+    assert in_bias is None or (in_bias.dtype == weight.dtype and in_bias.is_contiguous() and in_bias.numel() == x.shape[1])
     T, C = x.shape
     taps = weight.shape[1]
     assert x.dtype == torch.float32 and out.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
@@ -508,7 +603,7 @@ def causal_conv(x, weight, bias, carry, out, batch, *, silu=True):
     _call("cpi_causal_conv", _p(x), c_long(x.stride(0)), _p(weight), _p(bias), c_int(dtype_code(weight.dtype)),
           _p(carry), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_start),
           _p(batch.seq_tok0), _p(batch.seq_new), _p(out), c_long(out.stride(0)), c_int(T), c_int(batch.n_seqs),
-          c_int(C), c_int(taps), c_int(int(silu)), _stream())
+          c_int(C), c_int(taps), c_int(int(silu)), _p(in_bias), _stream())
     global launch_count
     launch_count += int(taps > 1)
 
@@ -731,7 +826,18 @@ def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq
           _p(sink), c_int(int(keep_first)), _stream())
 
 
-ROUTER_GATES = {"none": 0, "sigmoid": 1, "softmax_chosen": 2}
+ROUTER_GATES = {"none": 0, "sigmoid": 1, "softmax_chosen": 2, "sigmoid_normed": 3}
+
+
+def _rule(rule):
+    """The extra arguments of the selection: `rule` None, or for the gate "sigmoid_normed" a dictionary {"choice_bias":
+    float32 [experts] or None, "groups": n, "keep": n, "scale": s}: the choice is made on sigmoid(logit) + choice_bias
+    among the experts of the `keep` best of `groups` equal groups (a group's score: its two largest choice scores
+    summed), the weights are the chosen sigmoids divided by their sum and multiplied by `scale`."""
+    r = rule or {}
+    cb = r.get("choice_bias")
+    assert cb is None or (cb.dtype == torch.float32 and cb.is_contiguous() and cb.is_cuda)
+    return _p(cb), c_int(int(r.get("groups", 1))), c_int(int(r.get("keep", 1))), c_float(float(r.get("scale", 1.0)))
 
 
 def _gate_mode(sigmoid_gate) -> int:
@@ -739,7 +845,7 @@ def _gate_mode(sigmoid_gate) -> int:
     return ROUTER_GATES[sigmoid_gate] if isinstance(sigmoid_gate, str) else int(bool(sigmoid_gate))
 
 
-def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None, bias=None):
+def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None, bias=None, rule=None):
     _need_cuda(h, w, topk_idx, topk_gate, logits_out, bias)
     assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == w.shape[0])
     _rowmajor(h, "router h")
@@ -754,7 +860,8 @@ def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=No
         n = min(65535, T - t0)
         _call("cpi_router_topk", _p(h[t0:t0 + n]), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(logits_out[t0:t0 + n]), _p(topk_idx[t0:t0 + n]), _p(topk_gate[t0:t0 + n]),
-              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(_gate_mode(sigmoid_gate)), _p(bias), c_int(0), _stream())
+              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(_gate_mode(sigmoid_gate)), _p(bias), c_int(0),
+              *_rule(rule), _stream())
 
 
 def row_gates(h, w, out, bias=None):
@@ -769,11 +876,11 @@ def row_gates(h, w, out, bias=None):
         n = min(65535, T - t0)
         _call("cpi_router_topk", _p(h[t0:t0 + n]), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(out.view(T, E)[t0:t0 + n]), None, None, c_int(n), c_int(H), c_int(E), c_int(1),
-              c_int(0), _p(bias), c_int(1), _stream())
+              c_int(0), _p(bias), c_int(1), *_rule(None), _stream())
 
 
 def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, *, top_k,
-              sigmoid_gate, sorted_h=None, bias=None) -> bool:
+              sigmoid_gate, sorted_h=None, bias=None, rule=None) -> bool:
     """Router logits, the top-k choice and the per-expert row lists of a step; returns whether
     `sorted_h` (the activation rows in expert order) was filled too.  A step with few tokens takes two
     launches (logits, then one kernel for the rest), a larger one the separate kernels; the results
@@ -788,11 +895,11 @@ def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_s
         assert w.is_contiguous() and w.shape[1] == H and logits.dtype == torch.float32 and logits.is_contiguous()
         _call("cpi_router_topk", _p(h), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
               c_int(dtype_code(w.dtype)), _p(logits), None, None, c_int(T), c_int(H), c_int(E), c_int(top_k),
-              c_int(gm), _p(bias), c_int(0), _stream())
+              c_int(gm), _p(bias), c_int(0), *_rule(None), _stream())
         rc = load().cpi_moe_route_small(_p(logits), c_int(T), c_int(E), c_int(top_k), c_int(gm),
                                         _p(topk_idx), _p(topk_gate), _p(group_offsets), _p(row_token), _p(row_scale),
                                         _p(row_of_slot), _p(h), c_long(h.stride(0) * h.element_size()), _p(sorted_h),
-                                        c_int(H * h.element_size()), _stream())
+                                        c_int(H * h.element_size()), *_rule(rule), _stream())
         if rc == 0:
             global launch_count
             launch_count += 1
@@ -801,9 +908,10 @@ def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_s
             raise KernelError(load().cpi_last_error().decode())
         # too large or unaligned for the one-launch kernel: select here, lists below
         _call("cpi_router_select", _p(logits), _p(topk_idx), _p(topk_gate), c_int(T), c_int(E), c_int(top_k),
-              c_int(gm), _stream())
+              c_int(gm), *_rule(rule), _stream())
     else:
-        router_topk(h, w, topk_idx, topk_gate, top_k=top_k, sigmoid_gate=sigmoid_gate, logits_out=logits, bias=bias)
+        router_topk(h, w, topk_idx, topk_gate, top_k=top_k, sigmoid_gate=sigmoid_gate, logits_out=logits, bias=bias,
+                    rule=rule)
     moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot, n_tokens=T, top_k=top_k,
               n_experts=E)
     return False

@@ -136,9 +136,77 @@ router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __r
   }
 }
 
+// Mode 3 of the selection: scores s = sigmoid(logit); the choice is made on s + choice_bias (the bias never enters a
+// weight); the experts form `n_groups` equal groups of neighbours, a group's score is the sum of its two largest choice
+// scores, and only experts of the `keep_groups` best groups can be chosen; the weights are the chosen s divided by their
+// sum (+ 1e-20), times `gate_scale`.
+struct SelectRule {
+  int gate_mode;
+  const float* choice_bias;              // [experts] float32 or null
+  int n_groups, keep_groups;             // 1, 1: no groups
+  float gate_scale;
+};
+
+__device__ __forceinline__ void select_grouped(const float* lg, int* idx, float* gate, int n_experts, int top_k,
+                                               const SelectRule& r) {
+  auto choice = [&](int e) {
+    const float s = 1.0f / (1.0f + expf(-lg[e]));
+    return r.choice_bias ? s + r.choice_bias[e] : s;
+  };
+  const int per = n_experts / r.n_groups;
+  unsigned long long kept = ~0ull;
+  if (r.n_groups > 1 && r.keep_groups < r.n_groups) {
+    kept = 0ull;
+    for (int k = 0; k < r.keep_groups; ++k) {
+      int bg = -1;
+      float bs = 0.f;
+      for (int g = 0; g < r.n_groups; ++g) {
+        if ((kept >> g) & 1ull) continue;
+        float m1 = -INFINITY, m2 = -INFINITY;              // the group's two largest choice scores
+        for (int e = g * per; e < (g + 1) * per; ++e) {
+          const float c = choice(e);
+          if (c != c) continue;
+          if (c > m1) { m2 = m1; m1 = c; } else if (c > m2) { m2 = c; }
+        }
+        const float gs = per > 1 ? m1 + m2 : m1;
+        if (bg < 0 || gs > bs) { bg = g; bs = gs; }
+      }
+      kept |= 1ull << bg;
+    }
+  }
+  float sum = 0.f;
+  for (int k = 0; k < top_k; ++k) {
+    int best = -1;
+    float bv = 0.f;
+    for (int e = 0; e < n_experts; ++e) {
+      if (!((kept >> (e / per)) & 1ull)) continue;
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= (idx[j] == e);
+      if (taken) continue;
+      const float c = choice(e);
+      if (c != c) continue;
+      if (best < 0 || c > bv) { best = e; bv = c; }
+    }
+    if (best < 0) {                                        // nothing left to choose from: the lowest free index
+      for (int e = 0; e < n_experts && best < 0; ++e) {
+        bool taken = false;
+        for (int j = 0; j < k; ++j) taken |= (idx[j] == e);
+        if (!taken) best = e;
+      }
+    }
+    idx[k] = best;
+    gate[k] = 1.0f / (1.0f + expf(-lg[best]));
+    sum += gate[k];
+  }
+  const float f = r.gate_scale / (sum + 1e-20f);
+  for (int k = 0; k < top_k; ++k) gate[k] *= f;
+}
+
 // The k best logits of one token, ties to the lowest index; gate = 1 (mode 0), the sigmoid of the chosen logit
-// (mode 1), or the softmax over the chosen logits (mode 2).
-__device__ __forceinline__ void select_topk(const float* lg, int* idx, float* gate, int n_experts, int top_k, int gate_mode) {
+// (mode 1), or the softmax over the chosen logits (mode 2); mode 3: see SelectRule.
+__device__ __forceinline__ void select_topk(const float* lg, int* idx, float* gate, int n_experts, int top_k, const SelectRule& rule) {
+  const int gate_mode = rule.gate_mode;
+  if (gate_mode == 3) { select_grouped(lg, idx, gate, n_experts, top_k, rule); return; }
   for (int k = 0; k < top_k; ++k) {
     int best = -1;
     float bv = 0.f;
@@ -173,13 +241,13 @@ __device__ __forceinline__ void select_topk(const float* lg, int* idx, float* ga
 // One thread per token.
 __global__ void router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx,
                                      float* __restrict__ topk_gate, int n_tokens, int n_experts, int top_k,
-                                     int gate_mode) {
+                                     SelectRule rule) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tokens) return;
   select_topk(logits + (size_t)t * n_experts, topk_idx + (size_t)t * top_k, topk_gate + (size_t)t * top_k, n_experts,
-              top_k, gate_mode);
+              top_k, rule);
 }
 
 // A step with few tokens: selection, the per-expert row lists and the gather of the activation rows in
@@ -188,7 +256,7 @@ __global__ void router_select_kernel(const float* __restrict__ logits, int* __re
 // the same stable order as router_select_kernel + moe_lists_kernel.
 constexpr int kSmallSlots = 256, kSmallLogits = 4096;
 __global__ void __launch_bounds__(128)
-moe_route_small_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int gate_mode,
+moe_route_small_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, SelectRule rule,
                        int* __restrict__ topk_idx, float* __restrict__ topk_gate, int* __restrict__ group_offsets,
                        int* __restrict__ row_token, float* __restrict__ row_scale, int* __restrict__ row_of_slot,
                        const uint4* __restrict__ src, long src_stride16, uint4* __restrict__ dst, int chunks) {
@@ -201,7 +269,7 @@ moe_route_small_kernel(const float* __restrict__ logits, int n_tokens, int n_exp
   for (int i = tid; i < n_tokens * n_experts; i += 128) lg_s[i] = logits[i];
   __syncthreads();
   for (int t = tid; t < n_tokens; t += 128)
-    select_topk(lg_s + t * n_experts, idx_s + t * top_k, gate_s + t * top_k, n_experts, top_k, gate_mode);
+    select_topk(lg_s + t * n_experts, idx_s + t * top_k, gate_s + t * top_k, n_experts, top_k, rule);
   __syncthreads();
   for (int e = tid; e < n_experts; e += 128) {
     int c = 0;
@@ -303,6 +371,14 @@ moe_lists_kernel(const int* __restrict__ topk_idx, const float* __restrict__ top
 
 using namespace cpi;
 
+static int check_rule(const SelectRule& r, int n_experts) {
+  if (r.gate_mode != 3) return 0;
+  CPI_REQUIRE(r.n_groups >= 1 && r.n_groups <= 64 && n_experts % r.n_groups == 0 && r.keep_groups >= 1 &&
+              r.keep_groups <= r.n_groups, "router: %d experts in %d groups of which %d are kept (up to 64 equal groups)",
+              n_experts, r.n_groups, r.keep_groups);
+  return 0;
+}
+
 // gate_mode: 0 none (gates are 1), 1 sigmoid of the chosen logit, 2 softmax over the chosen logits.  `logits` is
 // float32 [n_tokens, n_experts] scratch that also serves as the optional output of the router logits; `bias`
 // (float32 [n_experts] or null) is added to them.  `sigmoid_out` (only without a selection, topk_idx null): what is
@@ -310,7 +386,8 @@ using namespace cpi;
 extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const void* w, int w_dtype,
                                float* logits, int* topk_idx, float* topk_gate, int n_tokens,
                                int hidden, int n_experts, int top_k, int gate_mode, const float* bias,
-                               int sigmoid_out, cudaStream_t stream) {
+                               int sigmoid_out, const float* choice_bias, int n_groups, int keep_groups,
+                               float gate_scale, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_experts >= 1 && n_experts <= kMaxExperts, "router: %d experts (supported: 1..%d)", n_experts, kMaxExperts);
   CPI_REQUIRE(top_k >= 1 && top_k <= n_experts, "router: top-k %d of %d experts", top_k, n_experts);
@@ -332,7 +409,9 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
   }
   if (check_launch("router_logits")) return 2;
   if (!topk_idx) return 0;                          // logits only: the caller selects in a later kernel
-  cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
+  SelectRule rule{gate_mode, choice_bias, n_groups, keep_groups, gate_scale};
+  if (check_rule(rule, n_experts)) return 1;
+  cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, rule);
   return check_launch("router_select");
 }
 
@@ -341,23 +420,29 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
 extern "C" int cpi_moe_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int gate_mode,
                                    int* topk_idx, float* topk_gate, int* group_offsets, int* row_token,
                                    float* row_scale, int* row_of_slot, const void* h, long h_stride_bytes,
-                                   void* sorted_h, int row_bytes, cudaStream_t stream) {
+                                   void* sorted_h, int row_bytes, const float* choice_bias, int n_groups,
+                                   int keep_groups, float gate_scale, cudaStream_t stream) {
   if (n_tokens <= 0 || (long)n_tokens * top_k > kSmallSlots || (long)n_tokens * n_experts > kSmallLogits ||
       n_experts > kMaxExperts || top_k < 1 || top_k > n_experts)
     return -1;
   if (sorted_h && (row_bytes % 16 || h_stride_bytes % 16 || (reinterpret_cast<uintptr_t>(h) & 15) ||
                    (reinterpret_cast<uintptr_t>(sorted_h) & 15)))
     return -1;
-  cpi::launch_pdl(moe_route_small_kernel, n_tokens * top_k, 128, 0, stream, logits, n_tokens, n_experts, top_k, gate_mode,
+  SelectRule rule{gate_mode, choice_bias, n_groups, keep_groups, gate_scale};
+  if (check_rule(rule, n_experts)) return 1;
+  cpi::launch_pdl(moe_route_small_kernel, n_tokens * top_k, 128, 0, stream, logits, n_tokens, n_experts, top_k, rule,
                   topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot,
                   sorted_h ? (const uint4*)h : (const uint4*)nullptr, h_stride_bytes / 16, (uint4*)sorted_h, row_bytes / 16);
   return check_launch("moe_route_small") ? 1 : 0;
 }
 
 extern "C" int cpi_router_select(const float* logits, int* topk_idx, float* topk_gate, int n_tokens, int n_experts,
-                                 int top_k, int gate_mode, cudaStream_t stream) {
+                                 int top_k, int gate_mode, const float* choice_bias, int n_groups, int keep_groups,
+                                 float gate_scale, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
+  SelectRule rule{gate_mode, choice_bias, n_groups, keep_groups, gate_scale};
+  if (check_rule(rule, n_experts)) return 1;
+  cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, rule);
   return check_launch("router_select");
 }
 

@@ -35,6 +35,7 @@ struct ConvParams {
   const int* seq_tok0; const int* seq_new;
   float* out; long out_stride;           // [T, C] float32
   int channels, taps, silu;
+  const void* in_bias;                   // [C] or null (w's dtype): added to every input of the step before it is used or carried
 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
@@ -49,10 +50,11 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(ConvParams p) {
   const int local = p.token_pos[t] - p.seq_start[s];          // tokens of this sequence before t in this step
   const float* carry = p.carry + (size_t)p.seq_slot[s] * (p.taps - 1) * p.channels;
   float acc = p.bias ? load_any(p.bias, p.w_dtype, c) : 0.f;
+  const float ib = p.in_bias ? load_any(p.in_bias, p.w_dtype, c) : 0.f;
   for (int j = 0; j < p.taps; ++j) {
     const int back = p.taps - 1 - j;                          // how many tokens before t
     float x;
-    if (back <= local) x = p.in[(size_t)(t - back) * p.in_stride + c];
+    if (back <= local) x = p.in[(size_t)(t - back) * p.in_stride + c] + ib;
     else x = carry[(size_t)(p.taps - 1 - (back - local)) * p.channels + c];
     acc = fmaf(load_any(p.w, p.w_dtype, (size_t)c * p.taps + j), x, acc);
   }
@@ -68,11 +70,12 @@ __global__ void __launch_bounds__(256) conv_carry_kernel(ConvParams p) {
   const int n = p.seq_new[s], tok0 = p.seq_tok0[s], keep = p.taps - 1;
   float* carry = p.carry + (size_t)p.seq_slot[s] * keep * p.channels;
   float v[CONV_MAX_TAPS];
+  const float ib = p.in_bias ? load_any(p.in_bias, p.w_dtype, c) : 0.f;
 #pragma unroll
   for (int j = 0; j < CONV_MAX_TAPS; ++j) {
     if (j < keep) {
       const int idx = n - keep + j;                           // index among this step's tokens; negative: an older input
-      v[j] = idx >= 0 ? p.in[(size_t)(tok0 + idx) * p.in_stride + c] : carry[(size_t)(j + n) * p.channels + c];
+      v[j] = idx >= 0 ? p.in[(size_t)(tok0 + idx) * p.in_stride + c] + ib : carry[(size_t)(j + n) * p.channels + c];
     }
   }
 #pragma unroll
@@ -508,20 +511,152 @@ static int dispatch_scan(const ScanParams& p, int n_seqs, int max_new, cudaStrea
   return 1;
 }
 
+
+// ---- a gated linear recurrent unit with one state per channel --------------------------------------------------
+//   r = sigmoid(g_r + b_r), i = sigmoid(g_i + b_i)          (g: the gates' block-diagonal products, computed before)
+//   log a = -rate * softplus(lam) * r,   S_t = a S_{t-1} + sqrt(1 - a^2) * i * u_t,   out_t = S_t * gelu_tanh(y_t + b_y)
+// all in float32; 1 - a^2 is taken as -expm1(2 log a), which keeps its digits when a is close to one.  A block takes
+// 32 channels of one sequence.  A step of many tokens is cut into `blockDim.y` runs of consecutive tokens: every run
+// is first scanned from a zero state (its product of decays and what it adds), the runs' results are chained in
+// shared memory, and a second pass repeats each run from its true entry state and writes the outputs.  A run of one
+// thread row (decode, short portions) is the recurrence as written.
+constexpr int RG_MAX_RUNS = 32;
+
+struct RgLruParams {
+  const float* gates; long gates_stride; // [blocks * T, 2 * block]: row b * T + t = block b's gate rows of token t (r, then i)
+  const void* r_bias; const void* i_bias; const void* lam; const void* y_bias; int small_dtype;      // [W] each; biases may be null
+  const float* u; long u_stride;         // [T, W] the recurrence's input
+  const float* y; long y_stride;         // [T, W] the other branch before its bias and activation
+  float* state;                          // [slots, W]
+  void* out; long out_stride;            // [T, W]
+  const int* seq_slot; const int* seq_tok0; const int* seq_new;
+  int n_tokens, width, block; float rate;
+};
+
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(1024) rglru_scan_kernel(RgLruParams p) {
+  pdl_launch_dependents();
+  __shared__ float A_s[RG_MAX_RUNS][32], B_s[RG_MAX_RUNS][32];
+  const int tx = threadIdx.x, j = threadIdx.y, runs = blockDim.y;
+  const int c = blockIdx.x * 32 + tx, s = blockIdx.y;
+  const bool live = c < p.width;
+  float b_r = 0.f, b_i = 0.f, b_y = 0.f, rate = 0.f;
+  if (live) {                                     // the channel's constants: no kernel writes them
+    if (p.r_bias) b_r = load_any(p.r_bias, p.small_dtype, c);
+    if (p.i_bias) b_i = load_any(p.i_bias, p.small_dtype, c);
+    if (p.y_bias) b_y = load_any(p.y_bias, p.small_dtype, c);
+    rate = -p.rate * softplus_f(load_any(p.lam, p.small_dtype, c));
+  }
+  pdl_wait();
+  const int n = p.seq_new[s], tok0 = p.seq_tok0[s];
+  const int len = (n + runs - 1) / runs;
+  const int t_lo = min(n, j * len), t_hi = min(n, t_lo + len);
+  const int cc = live ? c : 0;
+  const float* g = p.gates + ((size_t)(cc / p.block) * p.n_tokens + tok0) * p.gates_stride + cc % p.block;
+  const float* u = p.u + (size_t)tok0 * p.u_stride + cc;
+  auto gate = [&](int t, float& a, float& x) {
+    const float r = 1.0f / (1.0f + expf(-(g[(size_t)t * p.gates_stride] + b_r)));
+    const float i = 1.0f / (1.0f + expf(-(g[(size_t)t * p.gates_stride + p.block] + b_i)));
+    const float la = rate * r;
+    a = expf(la);
+    x = sqrtf(-expm1f(2.0f * la)) * (i * u[(size_t)t * p.u_stride]);
+  };
+  if (runs > 1) {
+    float A = 1.f, B = 0.f;
+    if (live)
+      for (int t = t_lo; t < t_hi; ++t) {
+        float a, x;
+        gate(t, a, x);
+        B = fmaf(a, B, x);
+        A *= a;
+      }
+    A_s[j][tx] = A; B_s[j][tx] = B;
+    __syncthreads();
+  }
+  if (!live) return;
+  float* st = p.state + (size_t)p.seq_slot[s] * p.width + c;
+  float S = *st;
+  for (int jj = 0; jj < j; ++jj) S = fmaf(A_s[jj][tx], S, B_s[jj][tx]);
+  const float* y = p.y + (size_t)tok0 * p.y_stride + c;
+  TO* o = reinterpret_cast<TO*>(p.out) + (size_t)tok0 * p.out_stride + c;
+  for (int t = t_lo; t < t_hi; ++t) {
+    float a, x;
+    gate(t, a, x);
+    S = fmaf(a, S, x);
+    o[(size_t)t * p.out_stride] = from_f32<TO>(S * gelu_tanh_f(y[(size_t)t * p.y_stride] + b_y));
+  }
+  if (j == runs - 1) *st = S;                      // the last run's exit state is the sequence's (an empty run passes it on)
+}
+
+
+// out[b * T + t, :] = in[t, b * n : (b + 1) * n] in out's dtype: the equal parts of float32 rows laid out part by part,
+// as the rows of a grouped product with one group per part; offsets[b] = b * T for b = 0 .. parts.
+template <typename TO>
+__global__ void __launch_bounds__(256) block_major_rows_kernel(const float* __restrict__ in, long in_stride,
+                                                               TO* __restrict__ out, int* __restrict__ offsets,
+                                                               int n_tokens, int parts, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float* src = in + (size_t)t * in_stride;
+  for (int i = threadIdx.x; i < parts * n; i += blockDim.x)
+    out[((size_t)(i / n) * n_tokens + t) * n + i % n] = from_f32<TO>(src[i]);
+  if (t == 0)
+    for (int b = threadIdx.x; b <= parts; b += blockDim.x) offsets[b] = b * n_tokens;
+}
+
 }  // namespace cpi
 
 using namespace cpi;
+
+extern "C" int cpi_block_major_rows(const float* in, long in_stride, void* out, int out_dtype, int* offsets,
+                                    int n_tokens, int parts, int n, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(parts >= 1 && n >= 1, "block_major_rows: %d parts of %d elements", parts, n);
+  CPI_DISPATCH_DTYPE(out_dtype, TO, cpi::launch_pdl(block_major_rows_kernel<TO>, dim3(n_tokens), dim3(256), 0, stream, in,
+                                                    in_stride, reinterpret_cast<TO*>(out), offsets, n_tokens, parts, n));
+  return check_launch("block_major_rows");
+}
+
+extern "C" int cpi_rglru_scan(const float* gates, long gates_stride, const void* r_bias, const void* i_bias,
+                              const void* lam, const void* y_bias, int small_dtype, const float* u, long u_stride,
+                              const float* y, long y_stride, float* state, void* out, int out_dtype, long out_stride,
+                              const int* seq_slot, const int* seq_tok0, const int* seq_new, int n_seqs, int max_new,
+                              int n_tokens, int width, int block, float rate, cudaStream_t stream) {
+  if (n_seqs == 0 || n_tokens == 0) return 0;
+  CPI_REQUIRE(width > 0 && block > 0 && width % block == 0, "rglru_scan: %d channels in blocks of %d", width, block);
+  CPI_REQUIRE(lam != nullptr, "rglru_scan: the channels' decay parameters are missing");
+  CPI_REQUIRE(n_seqs <= 65535, "rglru_scan: too many sequences in one step (%d)", n_seqs);
+  RgLruParams p{gates, gates_stride, r_bias, i_bias, lam, y_bias, small_dtype, u, u_stride, y, y_stride, state, out,
+                out_stride, seq_slot, seq_tok0, seq_new, n_tokens, width, block, rate};
+  // runs of at least 16 tokens, as many as fill the GPU twice over, at most RG_MAX_RUNS
+  int runs = 1;
+  if (max_new >= 32) {
+    const int blocks = n_seqs * ((width + 31) / 32);
+    runs = (2 * sm_count() * 2048 / 32 + blocks - 1) / blocks;
+    if (runs > max_new / 16) runs = max_new / 16;
+    if (runs > RG_MAX_RUNS) runs = RG_MAX_RUNS;
+    if (runs < 1) runs = 1;
+  }
+  const dim3 grid((width + 31) / 32, n_seqs), block_dim(32, runs);
+  CPI_DISPATCH_DTYPE(out_dtype, TO, cpi::launch_pdl(rglru_scan_kernel<TO>, grid, block_dim, 0, stream, p));
+  return check_launch("rglru_scan");
+}
 
 extern "C" int cpi_causal_conv(const float* in, long in_stride, const void* w, const void* bias, int w_dtype,
                                float* carry, const int* token_seq, const int* token_pos, const int* seq_slot,
                                const int* seq_start, const int* seq_tok0, const int* seq_new, float* out,
                                long out_stride, int n_tokens, int n_seqs, int channels, int taps, int silu,
-                               cudaStream_t stream) {
+                               const void* in_bias, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: %d taps (supported: 1 to %d)", taps, CONV_MAX_TAPS);
   CPI_REQUIRE(channels > 0 && n_seqs > 0, "causal_conv: bad sizes C=%d sequences=%d", channels, n_seqs);
   ConvParams p{in, in_stride, w, bias, w_dtype, carry, token_seq, token_pos, seq_slot, seq_start, seq_tok0, seq_new,
-               out, out_stride, channels, taps, silu};
+               out, out_stride, channels, taps, silu, in_bias};
   const int threads = channels <= 128 ? 128 : 256;
   cpi::launch_pdl(causal_conv_kernel, dim3(n_tokens, (channels + threads - 1) / threads), threads, 0, stream, p);
   if (int rc = check_launch("causal_conv")) return rc;

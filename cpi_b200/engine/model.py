@@ -144,6 +144,7 @@ class DecoderModel:
         # the residual: float32 [T, H], or [S, T, H] for blocks that keep S streams (each starts as the embedding)
         xs = self.ws.get("residual", (S, T, H), torch.float32)
         self.ws.pending_writeback = None
+        self.ws.residual_copy = None
         with phase("embedding"):
             if self.embed_norm is not None:                 # the looked-up rows are normed into the residual
                 raw = self.ws.get("embed_rows", (T, H), torch.float32)

@@ -3,3 +3,4 @@ from . import llama4  # noqa: F401
 from . import veredra  # noqa: F401
 from . import savenex  # noqa: F401
 from . import nogapel  # noqa: F401
+from . import kikerax  # noqa: F401

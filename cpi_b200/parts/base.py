@@ -60,9 +60,11 @@ class Norm(Part):
 @dataclass(frozen=True)
 class RotaryEncoding:
     """q and k are rotated pairwise: the pair d of a head at position p turns by the angle p * inv_freq[d]
-    (float32 [head_dim / 2] on the device); `interleaved` pairs (2d, 2d + 1), otherwise (d, d + head_dim / 2)."""
+    (float32 [head_dim / 2] on the device); `interleaved` pairs (2d, 2d + 1), otherwise (d, d + head_dim / 2);
+    `amplitude` multiplies every sine and cosine (a frequency rule that also rescales the rotated part)."""
     inv_freq: torch.Tensor
     interleaved: bool = False
+    amplitude: float = 1.0
 
 
 @dataclass(frozen=True)

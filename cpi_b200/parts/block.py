@@ -15,6 +15,12 @@ the workspace and done by the next layer's first kernel (or by `Workspace.settle
 residual first), so a layer costs as many of these launches as it has sublayers.  A layer without a feed-forward
 has the first sublayer only.
 
+"post_norm": x += norm1(mixer(x)); x += norm2(ffn(x)).  The sublayers read the residual itself (in the activation
+dtype); the norm acts on a sublayer's output, with the layer's norm weights.  One kernel per sublayer norms the output,
+adds it into the float32 residual and writes the next sublayer's input; the copy a layer's last sublayer leaves is the
+next layer's input when that layer is of this kind too.  A mixer that is a weighted sum of branches hands its branches
+over (`branch_outputs`), so that the sum, the norm and the addition are one pass.
+
 "scaled_pre_norm": x += m * mixer(norm1(x)); x += m * ffn(norm2(x)) with one constant m (`residual_scale`).  It is the
 arrangement above with a single stream and constant coefficients (read 1, mix 1, write m), so the scaled addition of a
 sublayer's output rides on the kernel that forms the next sublayer's normed input.
@@ -160,3 +166,56 @@ class ScaledPreNormBlock(HyperConnectionsBlock):
         one = torch.ones(1, dtype=torch.float32, device=device)
         c = (one, torch.full((1,), self.scale, dtype=torch.float32, device=device), one.view(1, 1).clone())
         self.coef = [c, c]
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """No params and no tensors of its own: the layer's norm parts give weight and eps."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix="", **_):
+        super().__init__(spec, prefix)
+
+    @staticmethod
+    def _input(ws, x, dtype):
+        """The residual in the activation dtype: x itself in float32, else the copy that the sublayer before left
+        (or a fresh one)."""
+        if dtype == torch.float32:
+            return x
+        T, H = x.shape
+        h = ws.get("post_norm_h", (T, H), dtype)
+        if ws.residual_copy != (x.data_ptr(), T, H, dtype):
+            K.cast_rows(x, h)
+        return h
+
+    @staticmethod
+    def _enter(ws, ys, scales, norm, x, dtype):
+        """x += rmsnorm(sum_b scales[b] ys[b]) * w, and the new x in the activation dtype for whoever reads it next."""
+        if norm.weight_offset:
+            raise ValueError("post_norm: a norm weight stored as a distance from a constant is not supported here")
+        h = None if dtype == torch.float32 else ws.get("post_norm_h", x.shape, dtype)
+        with phase("rmsnorm"):
+            K.sum_norm_add(ys, scales, norm.weight, x, eps=norm.eps, add=True, h_out=h)
+        ws.residual_copy = None if h is None else (x.data_ptr(), x.shape[0], x.shape[1], dtype)
+
+    def run(self, layer, residual, batch, cache):
+        ws, x = layer.mixer_norm.ws, residual
+        if x.dim() != 2:
+            raise ValueError("post_norm: the block keeps one residual stream")
+        keep, ws.residual_copy = ws.residual_copy, None
+        ws.settle()                         # (forgets the copy: whoever else settles has changed the residual)
+        ws.residual_copy = keep
+        T, H = x.shape
+        h = self._input(ws, x, batch.dtype)
+        outs = getattr(layer.mixer, "branch_outputs", lambda *a: None)(h, batch, cache)
+        if outs is None:
+            y = ws.get("post_norm_y", (T, H), torch.float32)
+            HyperConnectionsBlock._run_part(layer.mixer, h, y, batch, cache)
+            outs = ([y], [1.0])
+        self._enter(ws, outs[0], outs[1], layer.mixer_norm, x, batch.dtype)
+        if layer.feed_forward is None:
+            return
+        h = self._input(ws, x, batch.dtype)
+        y = ws.get("post_norm_y", (T, H), torch.float32)
+        HyperConnectionsBlock._run_part(layer.feed_forward, h, y, batch)
+        self._enter(ws, [y], [1.0], layer.feed_forward_norm, x, batch.dtype)

@@ -13,14 +13,18 @@ dense_swiglu  params: hidden_size, intermediate_size, activation ("silu" by defa
               tensors: feed_forward.{gate,up,down}_proj.weight
 moe_swiglu    params: hidden_size, num_experts, top_k, expert_size, shared_size (0 = no shared expert),
               router_gate ("sigmoid_input" | "sigmoid_output" | "none" | "softmax_chosen": the chosen experts'
-              outputs weighted by the softmax over their logits), router_bias (a tensor name [E] added to the logits,
+              outputs weighted by the softmax over their logits | "sigmoid_normed": with s = sigmoid(logits) the choice is
+              made on s + choice bias (`router_rule` {"choice_bias": a tensor name [E] or None, "groups": n, "keep": m,
+              "scale": c}; only experts of the m best of n equal groups of neighbours can be chosen, a group's score
+              being the sum of its two largest choice scores), and the chosen experts' outputs are weighted by their s
+              divided by the chosen s' sum, times c), router_bias (a tensor name [E] added to the logits,
               or None), expert_layout ("stacked", below, or "per_expert": `expert_names` {"gate", "up", "down"} with
               "{e}" for the expert's number, each [out, in]), router_name, shared (None or the params of a
               dense_swiglu part that runs for every token beside the routed experts, instead of shared_size)
               tensors: feed_forward.router.weight [E, H], feed_forward.experts.gate_up_proj [E, H, 2I],
               feed_forward.experts.down_proj [E, I, H], feed_forward.shared_expert.{gate,up,down}_proj.weight
 
-dense_mlp     params: hidden_size, intermediate_size, activation ("relu_squared": max(z, 0)^2), tensor_names (up, down):
+dense_mlp     params: hidden_size, intermediate_size, activation ("relu_squared": max(z, 0)^2, or "gelu_tanh"), tensor_names (up, down):
               down(act(up h)), no gate.  The activation acts on the float32 accumulator of the first product, so its
               input is rounded once, after it.
               tensors: feed_forward.{up,down}_proj.weight
@@ -36,7 +40,8 @@ from ..csrc import lib as K
 from ..phases import active as phases_active, phase
 from ..weights.store import TensorReq
 from .base import FeedForward, register_feed_forward
-from .linear import MODE_ADD, MODE_CLAMPED_GLU, MODE_GEGLU, MODE_STORE, MODE_STORE_RELU2, MODE_SWIGLU, project
+from .linear import (MODE_ADD, MODE_CLAMPED_GLU, MODE_GEGLU, MODE_STORE, MODE_STORE_GELU, MODE_STORE_RELU2, MODE_SWIGLU,
+                     project)
 
 
 def _stack(a, b):
@@ -111,7 +116,7 @@ class DenseSwiGLU(FeedForward):
 class DenseMLP(FeedForward):
     graph_safe = True
     can_store = True
-    ACTIVATIONS = ("relu_squared",)
+    ACTIVATIONS = {"relu_squared": MODE_STORE_RELU2, "gelu_tanh": MODE_STORE_GELU}
 
     def __init__(self, spec, prefix="", workspace=None):
         super().__init__(spec, prefix)
@@ -136,7 +141,7 @@ class DenseMLP(FeedForward):
         T = h.shape[0]
         with phase("mlp"):
             a = self.ws.get("mlp_act", (T, self.inter), h.dtype)
-            project(h, self.w_up, a, MODE_STORE_RELU2)          # the activation in the product's epilogue
+            project(h, self.w_up, a, self.ACTIVATIONS[self.activation])      # the activation in the product's epilogue
             project(a, self.w_down, residual, MODE_ADD if add else MODE_STORE)
 
 
@@ -149,8 +154,22 @@ class MoESwiGLU(FeedForward):
         self.hidden, self.n_experts, self.top_k = int(p["hidden_size"]), int(p["num_experts"]), int(p["top_k"])
         self.inter, self.shared_inter = int(p["expert_size"]), int(p.get("shared_size", 0))
         self.gate_mode = p.get("router_gate", "sigmoid_input")
-        if self.gate_mode not in ("sigmoid_input", "sigmoid_output", "none", "softmax_chosen"):
+        if self.gate_mode not in ("sigmoid_input", "sigmoid_output", "none", "softmax_chosen", "sigmoid_normed"):
             raise ValueError(f"moe_swiglu: unknown router_gate '{self.gate_mode}'")
+        rule = dict(p.get("router_rule") or {})
+        self.rule = None
+        self.n_choice_bias = None
+        if self.gate_mode == "sigmoid_normed":
+            groups, keep = int(rule.get("groups", 1)), int(rule.get("keep", 1))
+            if not (1 <= keep <= groups <= 64) or int(p["num_experts"]) % groups:
+                raise ValueError(f"moe_swiglu: {p['num_experts']} experts in {groups} groups of which {keep} are kept")
+            if int(p["top_k"]) > keep * (int(p["num_experts"]) // groups):
+                raise ValueError(f"moe_swiglu: top_k {p['top_k']} exceeds the experts of the {keep} kept groups")
+            self.rule = {"choice_bias": None, "groups": groups, "keep": keep, "scale": float(rule.get("scale", 1.0))}
+            if rule.get("choice_bias") is not None:
+                self.n_choice_bias = prefix + rule["choice_bias"]
+        elif rule:
+            raise ValueError("moe_swiglu: router_rule belongs to the gate 'sigmoid_normed'")
         if not 1 <= self.top_k <= self.n_experts:
             raise ValueError(f"moe_swiglu: top_k {self.top_k} of {self.n_experts} experts")
         if self.n_experts > 256:
@@ -195,6 +214,8 @@ class MoESwiGLU(FeedForward):
         reqs = [TensorReq(self.n_router, (self.n_experts, self.hidden))]
         if self.n_router_bias is not None:
             reqs.append(TensorReq(self.n_router_bias, (self.n_experts,)))
+        if self.n_choice_bias is not None:
+            reqs.append(TensorReq(self.n_choice_bias, (self.n_experts,)))
         if self.layout == "per_expert":
             for e in range(self.n_experts):
                 reqs += [TensorReq(self.expert_names["gate"].format(e=e), (self.inter, self.hidden)),
@@ -211,6 +232,8 @@ class MoESwiGLU(FeedForward):
         self.w_router = source.get(self.n_router, device).contiguous()
         if self.n_router_bias is not None:
             self.b_router = source.get(self.n_router_bias, device).to(torch.float32).contiguous()
+        if self.n_choice_bias is not None:
+            self.rule["choice_bias"] = source.get(self.n_choice_bias, device).to(torch.float32).contiguous()
         if self.layout == "per_expert":                                       # stored [out, in] already
             n = self.expert_names
             self.w_gate_up = torch.stack([_stack(source.get(n["gate"].format(e=e), device), source.get(n["up"].format(e=e), device))
@@ -251,7 +274,8 @@ class MoESwiGLU(FeedForward):
         with phase("moe_router"):
             gathered = K.moe_route(h, self.w_router, idx, gate, logits, offsets, row_token, row_scale, row_of_slot,
                                    top_k=Kk, sorted_h=sorted_h, bias=self.b_router,
-                                   sigmoid_gate="softmax_chosen" if self.gate_mode == "softmax_chosen" else self.gate_mode != "none")
+                                   sigmoid_gate=self.gate_mode if self.gate_mode in ("softmax_chosen", "sigmoid_normed")
+                                   else self.gate_mode != "none", rule=self.rule)
         if self.capture is not None:
             self.capture.append(idx.clone())
         hint = max(1, -(-M // E))
@@ -266,7 +290,7 @@ class MoESwiGLU(FeedForward):
             else:
                 project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token, row_scale=in_scale,
                         group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
-            out_scale = row_scale if self.gate_mode in ("sigmoid_output", "softmax_chosen") else None
+            out_scale = row_scale if self.gate_mode in ("sigmoid_output", "softmax_chosen", "sigmoid_normed") else None
             # One expert per token: the down projection can add straight into the residual rows.  Beside a shared
             # expert on the second stream that needs an order (two kernels adding into the same rows at once would
             # sum in whatever order they meet): in a step with many tokens the join comes before the down

@@ -11,7 +11,7 @@ import torch
 from ..csrc import lib as K
 
 MODE_STORE, MODE_ADD, MODE_SWIGLU, MODE_GEGLU = K.MODE_STORE, K.MODE_ADD, K.MODE_SWIGLU, K.MODE_GEGLU
-MODE_CLAMPED_GLU, MODE_STORE_RELU2 = K.MODE_CLAMPED_GLU, K.MODE_STORE_RELU2
+MODE_CLAMPED_GLU, MODE_STORE_RELU2, MODE_STORE_GELU = K.MODE_CLAMPED_GLU, K.MODE_STORE_RELU2, K.MODE_STORE_GELU
 
 # set to False to force the FP32-pipe kernel everywhere (tests compare the two)
 use_tensor_cores = True

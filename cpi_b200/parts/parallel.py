@@ -3,7 +3,8 @@
 "parallel"  params: branches (a list of {"name", "mixer": PartSpec}: tensors of a branch live under the mixer's prefix
             + name + "."), combine {"kind": "normed_mean", "eps", "weights": [tensor name per branch, under the mixer's
             prefix]}: out = (1 / n) sum_b rmsnorm(branch_b(h)) * weight_b, each branch divided by its own root mean
-            square over the model width.  ("sum": the plain sum of the branches, no tensors.)
+            square over the model width.  ("sum": the plain sum of the branches, no tensors.  {"kind": "weighted_sum",
+            "scales": [a constant per branch]}: out = sum_b scale_b * branch_b(h), no tensors either.)
 
 The branches do not depend on one another: in a step of few tokens the first runs on a second stream beside the
 others (inside a captured graph this becomes two chains side by side), each into a buffer of its own, and the sum
@@ -54,9 +55,12 @@ class ParallelMixer(Mixer):
         self.branches = [build_part("mixer", b["mixer"], prefix, workspace=workspace, owns_cache=owns_cache)
                          for b in p["branches"]]
         c = p.get("combine") or {"kind": "sum"}
-        if c["kind"] not in ("sum", "normed_mean"):
+        if c["kind"] not in ("sum", "normed_mean", "weighted_sum"):
             raise ValueError(f"parallel: unknown way of combining the branches '{c['kind']}'")
         self.normed = c["kind"] == "normed_mean"
+        self.scales = [float(x) for x in c["scales"]] if c["kind"] == "weighted_sum" else None
+        if self.scales is not None and len(self.scales) != len(self.branches):
+            raise ValueError("parallel: a weighted sum needs one constant per branch")
         self.eps = float(c.get("eps", 0.0))
         self.weight_names = [prefix + n for n in c.get("weights", [])] if self.normed else []
         if self.normed and len(self.weight_names) != len(self.branches):
@@ -95,10 +99,29 @@ class ParallelMixer(Mixer):
 
     def forward(self, h, residual, batch, cache, add=True):
         T = h.shape[0]
+        if self.scales is not None:
+            ys, scales = self.branch_outputs(h, batch, cache)
+            with phase("combine"):
+                K.sum_norm_add(ys, scales, None, residual, add=add, normalise=False)
+            return
         if not self.normed:
             for i, (n, b) in enumerate(zip(self.names, self.branches)):
                 b.forward(h, residual, batch, _BranchCache(cache, n), add=add or i > 0)
             return
+        ys = self._run_branches(h, batch, cache)
+        with phase("combine"):
+            K.branch_norm_sum(ys, self.weights, residual, eps=self.eps, scale=1.0 / len(ys), add=add)
+
+    def branch_outputs(self, h, batch, cache):
+        """(the branches' outputs, float32 [T, hidden] each, in workspace buffers; a constant per branch): the mixer's
+        output is their weighted sum, which a block that does something to that sum anyway may form itself.  None
+        unless the branches are combined by constants."""
+        if self.scales is None:
+            return None
+        return self._run_branches(h, batch, cache), self.scales
+
+    def _run_branches(self, h, batch, cache):
+        T = h.shape[0]
         ys = [self.ws.get(f"parallel_y{i}", (T, self.hidden), torch.float32) for i in range(len(self.branches))]
 
         def run(i):
@@ -130,5 +153,4 @@ class ParallelMixer(Mixer):
             run(i)
         if joined is not None:
             torch.cuda.current_stream().wait_event(joined)
-        with phase("combine"):
-            K.branch_norm_sum(ys, self.weights, residual, eps=self.eps, scale=1.0 / len(ys), add=add)
+        return ys

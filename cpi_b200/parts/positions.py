@@ -7,6 +7,8 @@ the device (the reference tabulates them, :466-470).  "none": q and k are used a
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -49,10 +51,30 @@ def llama3_frequencies_f64(dims: int, theta: float, scaling) -> np.ndarray:
     return f.astype(np.float32)
 
 
+def yarn_frequencies(dims: int, theta: float, scaling) -> tuple:
+    """(frequencies, amplitude) of the YaRN rule in double precision, rounded once.  With f_i = theta^(-2i / dims) and
+    d(t) = dims * ln(original / (2 pi t)) / (2 ln theta), the pair index whose wave makes t turns over `original`
+    positions: lo = max(floor(d(beta_fast)), 0), hi = min(ceil(d(beta_slow)), dims - 1), ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1); pair i turns at f_i (1 - ramp_i) + f_i / factor * ramp_i, so fast pairs keep their
+    frequency and slow pairs are stretched by `factor`; sines and cosines are multiplied by 0.1 ln(factor) + 1."""
+    factor, original = float(scaling["factor"]), float(scaling["original_max_position_embeddings"])
+    fast, slow = float(scaling["beta_fast"]), float(scaling["beta_slow"])
+    if not (factor > 0 and original > 0 and fast > 0 and slow > 0 and theta > 1):
+        raise ValueError("rope: the yarn rule needs positive factor, original length, beta_fast and beta_slow")
+    i = np.arange(dims // 2, dtype=np.float64)
+    f = np.float64(theta) ** (-2.0 * i / dims)
+    turn = lambda t: dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+    lo, hi = max(math.floor(turn(fast)), 0), min(math.ceil(turn(slow)), dims - 1)
+    ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return (f / factor * ramp + f * (1.0 - ramp)).astype(np.float32), 0.1 * math.log(factor) + 1.0
+
+
 @register_position("rope")
 class RotaryPosition(Position):
     """params: head_dim, theta, pairing ("half_split" pairs (d, d+D/2); "interleaved" pairs (2d, 2d+1)),
-    scaling (None, the llama3 dictionary, or {"rope_type": "linear", "factor": f}: every frequency divided by f), rotary_dims (None: the whole head; n: only the first n elements of a
+    scaling (None, the llama3 dictionary, {"rope_type": "linear", "factor": f}: every frequency divided by f, or
+    {"rope_type": "yarn", "factor", "original_max_position_embeddings", "beta_fast", "beta_slow"}: see
+    `yarn_frequencies`), rotary_dims (None: the whole head; n: only the first n elements of a
     head turn, as pairs (d, d + n/2) with frequencies theta^(-2d/n), the rest pass unchanged), frequency_math
     ("float32": the powers as the reference computes them; "float64": in double precision, rounded once, the
     llama3 rule included)."""
@@ -61,7 +83,9 @@ class RotaryPosition(Position):
     def __init__(self, spec, prefix=""):
         super().__init__(spec, prefix)
         sc = spec.get("scaling")
-        linear = None
+        linear, yarn = None, None
+        if sc is not None and sc.get("rope_type", "llama3") == "yarn":
+            yarn, sc = sc, None
         if sc is not None and sc.get("rope_type", "llama3") == "linear":
             linear, sc = float(sc["factor"]), None         # every frequency divided by one factor
             if not linear > 0:
@@ -75,7 +99,10 @@ class RotaryPosition(Position):
         dims = int(spec["head_dim"]) if dims is None else int(dims)
         if dims < 2 or dims % 2 or dims > int(spec["head_dim"]):
             raise ValueError(f"rope: {dims} rotated elements of a head of {spec['head_dim']}")
-        if spec.get("frequency_math", "float32") == "float64" and sc is not None:
+        self.amplitude = 1.0
+        if yarn is not None:
+            self.frequencies, self.amplitude = yarn_frequencies(dims, float(spec["theta"]), yarn)
+        elif spec.get("frequency_math", "float32") == "float64" and sc is not None:
             self.frequencies = llama3_frequencies_f64(dims, float(spec["theta"]), sc)
         elif spec.get("frequency_math", "float32") == "float64":
             # theta^(-2d/n) / factor in double precision, rounded once
@@ -91,7 +118,7 @@ class RotaryPosition(Position):
         self.inv_freq = torch.from_numpy(self.frequencies).to(device)
 
     def encoding(self):
-        return RotaryEncoding(self.inv_freq, self.interleaved)
+        return RotaryEncoding(self.inv_freq, self.interleaved, self.amplitude)
 
 
 @register_position("none")

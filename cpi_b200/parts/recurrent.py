@@ -20,6 +20,8 @@ in both precisions; the projections feed them as float32 rows.
           params: hidden_size, heads, key_dim (rows), value_dim (columns), tau, decay_rank, norm_eps,
           tensor_names {"q", "k", "v", "g", "o", "norm", "a1", "a2", "a2_bias"}.
           state: "s" [heads, key_dim, value_dim].
+
+"rglru" keeps a vector instead of a matrix: one state element per channel, see `RGLRUMixer`.
 """
 from __future__ import annotations
 
@@ -279,3 +281,92 @@ class GatedDeltaMixer(Mixer):
             K.gated_norm(o, gate, self.w_norm, g, parts=self.nh, gate_first=False, eps=self.eps, gate_act="sigmoid")
         with phase("wo"):
             project(g, self.w_o, residual, MODE_ADD if add else MODE_STORE)
+
+
+@register_mixer("rglru")
+class RGLRUMixer(Mixer):
+    """A recurrent block around a real-gated linear recurrent unit: two branches of `width` channels,
+
+        y = gelu_tanh(W_y h + b_y);   u = conv(W_x h + b_x)   (a causal convolution per channel with a bias, no activation);
+        per block b of `blocks` equal parts of u:  r = sigmoid(A_b u_b + a_b),  i = sigmoid(I_b u_b + i_b);
+        log a = -decay_scale * softplus(lam) * r;   S <- a S + sqrt(1 - a^2) (i u);   out = W_o (S y).
+
+    params: hidden_size, width, blocks, conv (taps), decay_scale (8 by default),
+    tensor_names {"y", "y_bias", "x", "x_bias", "conv", "conv_bias", "ra", "ra_bias", "ri", "ri_bias", "lam", "o"}
+    (ra, ri: [blocks, n, n] as [out, in]; their biases [blocks, n]).
+    state: "s" [width] float32, "conv" [conv - 1, width] (the last inputs of the convolution, biases included).
+    The gates' products take u in the activation dtype; the gates themselves, the decay with its softplus and
+    exponential, sqrt(1 - a^2), the state and the product S y are float32 in both precisions."""
+    graph_safe = True
+    can_store = True
+
+    def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.width, self.blocks = int(p["hidden_size"]), int(p["width"]), int(p["blocks"])
+        self.taps, self.rate = int(p.get("conv") or 1), float(p.get("decay_scale", 8.0))
+        if self.blocks < 1 or self.width % self.blocks:
+            raise ValueError(f"rglru: {self.width} channels cannot be cut into {self.blocks} equal blocks")
+        if not 1 <= self.taps <= 8:
+            raise ValueError(f"rglru: a convolution of {self.taps} taps (supported: 1 to 8)")
+        if not owns_cache:
+            raise ValueError("rglru: a recurrent layer cannot read another run entry's state")
+        self.n = self.width // self.blocks
+        tn = {"y": "mixer.y_proj.weight", "y_bias": "mixer.y_proj.bias", "x": "mixer.x_proj.weight",
+              "x_bias": "mixer.x_proj.bias", "conv": "mixer.conv1d.weight", "conv_bias": "mixer.conv1d.bias",
+              "ra": "mixer.recurrent_gate.weight", "ra_bias": "mixer.recurrent_gate.bias",
+              "ri": "mixer.input_gate.weight", "ri_bias": "mixer.input_gate.bias", "lam": "mixer.recurrent_param",
+              "o": "mixer.out_proj.weight"}
+        tn.update(p.get("tensor_names") or {})
+        self.tn = {k: prefix + v for k, v in tn.items()}
+        self.ws = workspace
+        self.w_in = self.b_y = self.b_x = self.w_conv = self.b_conv = self.w_gates = self.b_r = self.b_i = None
+        self.lam = self.w_o = None
+
+    def requirements(self):
+        t, H, W, B, n = self.tn, self.hidden, self.width, self.blocks, self.n
+        return [TensorReq(t["y"], (W, H)), TensorReq(t["y_bias"], (W,)), TensorReq(t["x"], (W, H)),
+                TensorReq(t["x_bias"], (W,)), TensorReq(t["conv"], (W, self.taps), init="const:0.3+normal"),
+                TensorReq(t["conv_bias"], (W,)), TensorReq(t["ra"], (B, n, n)), TensorReq(t["ra_bias"], (B, n)),
+                TensorReq(t["ri"], (B, n, n)), TensorReq(t["ri_bias"], (B, n)), TensorReq(t["lam"], (W,)),
+                TensorReq(t["o"], (H, W))]
+
+    def load(self, source, device):
+        t = self.tn
+        f32 = lambda name: source.get(t[name], device).to(torch.float32).reshape(-1).contiguous()
+        self.w_in = _cat_rows([source.get(t["y"], device), source.get(t["x"], device)])          # [2 W, H]
+        self.b_y, self.b_x, self.b_conv = f32("y_bias"), f32("x_bias"), f32("conv_bias")
+        self.w_conv = source.get(t["conv"], device).to(torch.float32).contiguous()
+        ra, ri = source.get(t["ra"], device), source.get(t["ri"], device)
+        dt = torch.float32 if torch.float32 in (ra.dtype, ri.dtype) else torch.bfloat16
+        self.w_gates = torch.cat([ra.to(dt), ri.to(dt)], dim=1).contiguous()                      # [blocks, 2 n, n]
+        self.b_r, self.b_i, self.lam = f32("ra_bias"), f32("ri_bias"), f32("lam")
+        self.w_o = source.get(t["o"], device).contiguous()
+
+    def state_requirements(self):
+        return [StateRequirement("s", (self.width,)), StateRequirement("conv", (max(self.taps - 1, 0), self.width))]
+
+    def forward(self, h, residual, batch, cache, add=True):
+        T, f32, W, B, n = h.shape[0], torch.float32, self.width, self.blocks, self.n
+        proj = self.ws.get("rglru_proj", (T, 2 * W), f32)                  # [y | x] before their biases
+        with phase("qkv"):
+            project(h, self.w_in, proj)
+        u = self.ws.get("rglru_u", (T, W), f32)
+        with phase("conv"):
+            K.causal_conv(proj[:, W:], self.w_conv, self.b_conv, cache.state("conv"), u, batch, silu=False,
+                          in_bias=self.b_x)
+        # the gates: a block-diagonal product, run as a grouped product with one group per block over u's blocks
+        # laid out block by block
+        ub = self.ws.get("rglru_ub", (B * T, n), h.dtype)
+        offsets = self.ws.get("rglru_offsets", (B + 1,), torch.int32)
+        gates = self.ws.get("rglru_gates", (B * T, 2 * n), f32)
+        with phase("gates"):
+            K.block_major_rows(u, ub, offsets, parts=B)
+            project(ub, self.w_gates, gates, MODE_STORE, m_rows=B * T, group_offsets=offsets, n_groups=B,
+                    rows_per_group_hint=T)
+        out = self.ws.get("rglru_out", (T, W), h.dtype)
+        with phase("scan"):
+            K.rglru_scan(gates, u, proj[:, :W], cache.state("s"), out, batch, block=n, lam=self.lam, r_bias=self.b_r,
+                         i_bias=self.b_i, y_bias=self.b_y, rate=self.rate)
+        with phase("wo"):
+            project(out, self.w_o, residual, MODE_ADD if add else MODE_STORE)

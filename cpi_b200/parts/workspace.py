@@ -13,9 +13,14 @@ class Workspace:
         # block fuses it with its first read): (streams x, y, write weights, mixing matrix) or None.  Whoever
         # reads the residual without knowing about it calls `settle()` first.
         self.pending_writeback = None
+        # A block whose sublayers read the residual itself may leave a copy of it in the activation dtype for the next
+        # block: (address, tokens, width, dtype) of the residual that the buffer "post_norm_h" mirrors, or None.
+        # `settle()` forgets it, so anything else that touches the residual in between invalidates the copy.
+        self.residual_copy = None
 
     def settle(self) -> None:
         """Applies a write-back that a block has left pending (see `pending_writeback`)."""
+        self.residual_copy = None
         p, self.pending_writeback = self.pending_writeback, None
         if p is not None:
             from ..csrc import lib as K
