@@ -864,6 +864,17 @@ def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=No
               *_rule(rule), _stream())
 
 
+def router_select(logits, topk_idx, topk_gate, *, top_k, sigmoid_gate, rule=None):
+    """The choice alone, from float32 router logits [T, E] (contiguous): the `top_k` experts of every token and their
+    weights, by the gate `sigmoid_gate` names (see ROUTER_GATES and `_rule`)."""
+    _need_cuda(logits, topk_idx, topk_gate)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and topk_idx.dtype == torch.int32
+    assert topk_gate.dtype == torch.float32 and topk_idx.numel() == T * top_k == topk_gate.numel()
+    _call("cpi_router_select", _p(logits), _p(topk_idx), _p(topk_gate), c_int(T), c_int(E), c_int(top_k),
+          c_int(_gate_mode(sigmoid_gate)), *_rule(rule), _stream())
+
+
 def row_gates(h, w, out, bias=None):
     """out[t, e] = sigmoid(h[t] . w[e] (+ bias[e])) in float32, the router's dot products in one launch: a gate per
     token and row of w (w [E, H], out float32 [T, E])."""

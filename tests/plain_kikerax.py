@@ -211,7 +211,9 @@ def router_choice(z, correction, r):
     return idx, w / (w.sum() + 1e-20) * float(r.get("scale", 1.0))
 
 
-def routed_ff(h, W, pre, mlp):
+def routed_ff(h, W, pre, mlp, forced=None, own=None):
+    """`forced` ([T, top] expert numbers): these experts are used instead of the router's own choice, with the weights
+    their scores give; `own` (a list) receives the router's own choices either way."""
     T = h.shape[0]
     r = mlp["router"]
     z = lin(W, pre + "router", h)
@@ -219,6 +221,12 @@ def routed_ff(h, W, pre, mlp):
     out = torch.zeros(T, h.shape[1], dtype=F)
     for t in range(T):
         idx, w = router_choice(z[t], corr, r)
+        if own is not None:
+            own.append(sorted(idx.tolist()))
+        if forced is not None:
+            idx = torch.as_tensor(forced[t], dtype=torch.long)
+            w = torch.sigmoid(z[t])[idx]
+            w = w / (w.sum() + 1e-20) * float(r.get("scale", 1.0))
         for e, we in zip(idx.tolist(), w):
             out[t] += we * gated_expert(h[t:t + 1], W, f"{pre}e{e}.")[0]
     if mlp.get("shared"):
@@ -227,8 +235,10 @@ def routed_ff(h, W, pre, mlp):
 
 
 # ---- the model ---------------------------------------------------------------------------------------------------
-def forward(cfg, W, tokens, layers_out=None):
-    """Logits [T, vocab] of one sequence from its first token; `layers_out` (a list) receives x after every layer."""
+def forward(cfg, W, tokens, layers_out=None, forced=None, own_choices=None):
+    """Logits [T, vocab] of one sequence from its first token; `layers_out` (a list) receives x after every layer.
+    `forced` {layer: [T, top]} replaces the routers' choices in those layers, `own_choices` (a dictionary) receives
+    every routed layer's own choices."""
     eps = float(cfg["norm"]["eps"])
     x = W["embed"].to(F)[torch.as_tensor(tokens, dtype=torch.long)]
     for i, L in enumerate(cfg["layers"]):
@@ -242,7 +252,11 @@ def forward(cfg, W, tokens, layers_out=None):
         x = x + rms(y, eps) * W[pre + "norm1"].to(F)
         mlp = L.get("mlp")
         if mlp:
-            y = dense_ff(x, W, pre + "mlp.") if mlp["kind"] == "dense" else routed_ff(x, W, pre + "mlp.", mlp)
+            if mlp["kind"] == "dense":
+                y = dense_ff(x, W, pre + "mlp.")
+            else:
+                own = None if own_choices is None else own_choices.setdefault(i, [])
+                y = routed_ff(x, W, pre + "mlp.", mlp, None if forced is None else forced.get(i), own)
             x = x + rms(y, eps) * W[pre + "norm2"].to(F)
         if layers_out is not None:
             layers_out.append(x.clone())
