@@ -44,6 +44,10 @@ gated-linear-attention layers at the same sizes, measured the same way.
 attention over a cached latent; norm once, mixer and squared-relu feed-forward side by side; a gated per-token input
 after every layer) at two layer sizes beside Veredra's windowed-attention layers at the same sizes, measured the
 same way.
+`--workload kikerax`: the Kikerax design (differential attention under a chunk mask alternating with a pair of
+soft-capped attention over its own keys and a gated linear recurrent unit; norms on the sublayers' outputs; gelu
+feed-forwards and experts chosen from the best groups) at two layer sizes beside Savenex's layers (attention beside a
+gated delta rule, dense and routed feed-forwards) at the same sizes, measured the same way.
 """
 from __future__ import annotations
 
@@ -991,6 +995,135 @@ def run_nogapel(args) -> dict:
     return out
 
 
+KIKERAX_SIZES = {
+    # width, dense ff, experts (count, top, ff each, shared ff, groups, kept), attention heads (heads, kv heads, head
+    # size = value size, chunk), the recurrent unit (channels, blocks, taps): two points with the layer shapes of 1-3 B
+    # and 7-8 B parameter models
+    "w2048": dict(width=2048, ff=8192, moe=(16, 2, 2048, 2048, 4, 2), attn=(16, 4, 128, 1024), unit=(2048, 16, 4)),
+    "w4096": dict(width=4096, ff=14336, moe=(16, 2, 3584, 3584, 4, 2), attn=(32, 8, 128, 2048), unit=(4096, 16, 4)),
+}
+
+
+def kikerax_config(sz: dict, vocab: int, pairs: int) -> dict:
+    """(differential attention + dense feed-forward, pair + routed experts) x pairs."""
+    H, G, D, chunk = sz["attn"]
+    C, blocks, taps = sz["unit"]
+    E, top, eff, sff, groups, keep = sz["moe"]
+    diff = {"type": "attention", "mlp": {"kind": "dense", "ff": sz["ff"]},
+            "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "diff": 0.5, "mask": {"size": chunk},
+                      "rot": {"base": 1e6, "dims": D // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    pair = {"type": "parallel",
+            "mlp": {"kind": "moe", "expert": {"ff": eff}, "shared": {"ff": sff},
+                    "router": {"experts": E, "top": top, "scale": 2.0, "groups": {"count": groups, "keep": keep}}},
+            "mixer": {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 30.0,
+                               "q_temp": {"coef": 0.1, "every": 1024}},
+                      "right": {"width": C, "blocks": blocks, "conv": taps}, "left_scale": 0.7, "right_scale": 0.7}}
+    return {"architecture": "Kikerax", "layers": [diff, pair] * pairs, "norm": {"eps": 1e-6}, "vocab": vocab,
+            "width": sz["width"], "logit_softcap": 30.0}
+
+
+def savenex_like_kikerax_config(sz: dict, vocab: int, layers: int) -> dict:
+    """The closest model the library had: Savenex layers (attention beside a gated delta rule; dense and routed
+    feed-forwards alternating) at the same width, head counts, head size, expert sizes; the attention sees everything,
+    the delta rule's state has as many value channels as the recurrent unit has channels."""
+    H, G, D, _ = sz["attn"]
+    C, _, taps = sz["unit"]
+    E, top, eff, sff, _, _ = sz["moe"]
+    mixer = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"base": 1e6, "dims": D}},
+             "right": {"heads": C // 256, "kv_heads": max(1, C // 512), "dim": 128, "vdim": 256, "conv": taps}}
+    dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}, "shared": {"ff": sff}}
+    return {"architecture": "Savenex", "layers": [{"type": "parallel", "mixer": mixer, "mlp": m} for m in (dense, moe) * (layers // 2)],
+            "norm": {"eps": 1e-6}, "vocab": vocab, "width": sz["width"]}
+
+
+def run_kikerax(args) -> dict:
+    """Prefill and decode of Kikerax at two layer sizes beside Savenex layers at equal sizes, with the time of every
+    phase per layer that has it and each phase's share of its roofline: products by flops over the measured bf16 rate in
+    prefill and by weight bytes over the measured copy rate in decode; attention by flops / cache bytes; recurrences and
+    row kernels by bytes."""
+    import torch
+
+    pk = peaks()
+    vocab, T, B, pairs = 32000, 2048, 8, 2
+    n_layers = 2 * pairs
+    g = torch.Generator().manual_seed(7)
+    toks = lambda n: torch.randint(0, vocab, (n,), generator=g).tolist()
+    out = {"metric": "tokens/s, Kikerax beside Savenex layers at equal layer sizes (bf16, random weights)",
+           "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "peaks": pk, "points": {}}
+    tf, bw = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    sizes = {k: v for k, v in KIKERAX_SIZES.items() if not args.sizes or k in args.sizes.split(",")}
+    for name, sz in sizes.items():
+        W, ff = sz["width"], sz["ff"]
+        H, G, D, chunk = sz["attn"]
+        C, blocks, taps = sz["unit"]
+        E, top, eff, sff, _, _ = sz["moe"]
+        kik = measure_config(kikerax_config(sz, vocab, pairs), vocab, T, B, toks)
+        sav = measure_config(savenex_like_kikerax_config(sz, vocab, n_layers), vocab, T, B, toks)
+        kp, kd = kik["phases_ms"]["prefill"], kik["phases_ms"]["decode_per_step"]
+        sp, sd = sav["phases_ms"]["prefill"], sav["phases_ms"]["decode_per_step"]
+
+        def frac(ms, flops=0.0, nbytes=0.0):
+            return None if not ms else round(max(flops / tf, nbytes / bw) / (ms / 1e3), 4)
+
+        def both(km, k_work, sm, s_work, per_k, per_s=n_layers):
+            get = lambda ph, names: sum(ph.get(n, 0) for n in names)
+            res = {"kikerax": {"prefill": frac(get(kp, km) / per_k, *k_work[0]), "decode": frac(get(kd, km) / per_k, *k_work[1])}}
+            if sm is not None:
+                res["savenex"] = {"prefill": frac(get(sp, sm) / per_s, *s_work[0]), "decode": frac(get(sd, sm) / per_s, *s_work[1])}
+            return res
+
+        ctx = T - 64
+        keys_all = T * (T + 1) // 2
+        keys_chunk = sum(t % chunk + 1 for t in range(T))
+        # per layer pair: two maps under the chunk mask, one map over everything
+        k_attn_flops = 4.0 * D * H * (2 * keys_chunk + keys_all)
+        k_attn_dec = B * G * D * 2.0 * (3 * (ctx % chunk + 1) + 2 * ctx)       # k, k2, v of the chunk; k, v of everything
+        s_attn_flops, s_attn_dec = 4.0 * D * H * keys_all, B * ctx * G * 2 * D * 2.0
+        n = C // blocks
+        d_proj = (2 * (H + G) * D + G * D + H + H * D) * W                      # q, k of two maps, v, gates, o
+        l_proj = ((H + G) * D + H + H * D) * W                                  # q, k, gates, o
+        u_proj = 3 * C * W + 2 * C * n                                          # y, x, o, the two block-diagonal gates
+        rh, rg = C // 256, max(1, C // 512)
+        s_proj = ((H + 2 * G) * D + H * D) * W + ((2 * rg * 128 + rh * 256 + rh + 32) * W + 16 * (rh * 128 + rh * 256) + rh * 256 * W)
+        dense_params = 2.0 * W * ff
+        s_dense_params = 3.0 * W * ff
+        touched = min(E, B * top) * 0.8
+        roof = {
+            "attention (two maps under a chunk mask, one soft-capped map over everything / one map over everything; tensor-core kernels)": both(
+                ["attention"], ((k_attn_flops,), (0.0, k_attn_dec)), ["attention"], ((s_attn_flops,), (0.0, s_attn_dec)), per_k=pairs),
+            "recurrence (gated linear recurrent unit, rglru_scan / gated delta rule, linear_scan)": both(
+                ["scan"], ((0.0, T * C * (4 * 4 + 2.0)), (0.0, B * C * (4 * 6 + 2.0))),
+                ["scan"], ((0.0, T * (2 * rg * 128 + rh * 128 + 2 * rh * 256 + rh) * 4.0), (0.0, B * rh * 128 * 256 * 8.0)), per_k=pairs),
+            "mixer projections in and out (with the unit's gate products)": both(
+                ["qkv", "wo", "gates"], ((2.0 * T * (d_proj + l_proj + u_proj),), (0.0, 2.0 * (d_proj + l_proj + u_proj))),
+                ["qkv", "wo"], ((2.0 * T * s_proj,), (0.0, 2.0 * s_proj)), per_k=pairs),
+            "row kernels of the mixers (norm, rotation, cache write, what follows attention per head, convolution / rotation, cache write, convolution, unit vectors, gated norm, branch sum)": both(
+                ["kv_store", "head_post", "conv"],
+                ((0.0, T * ((2 * (H + G) * D + G * D) * (4 + 2.0) + (H + G) * D * (4 + 2.0) + 3 * H * D * 2 * 2.0 + C * 8.0)),) * 2,
+                ["kv_store", "conv", "gated_norm", "combine"],
+                ((0.0, T * 4.0 * ((H + 2 * G) * D * 1.5 + 4 * (2 * rg * 128 + rh * 256) + 3.5 * rh * 256 + 3 * W)),) * 2, per_k=pairs),
+            "dense feed-forward and the shared expert (gelu in the up product's epilogue, silu gate / clamped and silu gates)": both(
+                ["mlp"], ((2.0 * T * (dense_params + 3.0 * W * sff),), (0.0, 2.0 * (dense_params + 3.0 * W * sff))),
+                ["mlp"], ((2.0 * T * (s_dense_params + 3.0 * W * sff),), (0.0, 2.0 * (s_dense_params + 3.0 * W * sff))),
+                per_k=pairs, per_s=n_layers / 2),
+            "routed experts (choice from the best groups / the best logits; the same grouped products)": both(
+                ["moe_router", "moe_expert", "moe_merge"], ((2.0 * T * 3.0 * W * top * eff,), (0.0, 2.0 * touched * 3.0 * W * eff)),
+                ["moe_router", "moe_expert", "moe_merge"], ((2.0 * T * 3.0 * W * top * eff,), (0.0, 2.0 * touched * 3.0 * W * eff)),
+                per_k=pairs, per_s=n_layers / 2),
+            "norms and the residual (one kernel per sublayer: sum, norm, add, next input / hc_step with one stream)": both(
+                ["rmsnorm"], ((0.0, T * W * (4 + 4 + 4 + 2.0)),) * 2, ["rmsnorm"], ((0.0, T * W * 2 * (4 + 4 + 4 + 2.0) / 2),) * 2,
+                per_k=2 * n_layers, per_s=2 * n_layers),
+        }
+        out["points"][name] = {"sizes": sz, "layers": n_layers, "prefill_tokens": T, "decode_batch": B, "decode_context": ctx,
+                               "kikerax": kik, "savenex": sav, "fraction_of_roofline": roof}
+    big = out["points"][sorted(out["points"])[-1]]
+    out["value"] = big["kikerax"]["decode_tok_s"]
+    out["config"] = {"model": "Kikerax, (differential attention + dense, attention beside a recurrent unit + routed experts) x 2",
+                     "global_batch": B, "seq_len": T, "parallelism": "single GPU", "l2": "weights of a step exceed the L2"}
+    return out
+
+
 def reference_arm_reason() -> str:
     """Why `--impl reference` has nothing to run, as found on this image (one line)."""
     return ("kurulav1/cpi is a CMake C++/CUDA project (no setup.py or pyproject.toml, so pip has nothing to install); "
@@ -1010,8 +1143,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--sizes", default="", help="--workload nogapel: a comma-separated subset of its size points")
-    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra", "savenex", "nogapel"],
+    ap.add_argument("--sizes", default="", help="--workload nogapel | kikerax: a comma-separated subset of its size points")
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline", "veredra", "savenex", "nogapel", "kikerax"],
                     default="scout24")
     ap.add_argument("--reference-root", default=os.environ.get("CPI_REFERENCE_ROOT"),
                     help="a checkout of kurulav1/cpi (for --workload cpu_baseline)")
@@ -1031,6 +1164,9 @@ def main() -> int:
         return 0
     if args.workload == "savenex":
         print(json.dumps(run_savenex(args)))
+        return 0
+    if args.workload == "kikerax":
+        print(json.dumps(run_kikerax(args)))
         return 0
     if args.workload == "nogapel":
         print(json.dumps(run_nogapel(args)))

@@ -40,6 +40,7 @@ struct Params {
   int* error_flag;                                  // set to 1 when a wait on the copy engine ran out
   const float* sink;                                // [NH] float32 or null: exp(sink[h]) joins the denominator
   int keep_first;                                   // sliding window: a sequence's first positions stay visible
+  float cap_in, cap_out;                            // soft cap c > 0 on the scaled scores: scale / c and c log2(e); else 0
 };
 
 constexpr uint32_t kSpinLimit = 1u << 24;
@@ -318,7 +319,9 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
       for (int e = 0; e < 4; ++e) {
         const int kp = kbase + nt * 8 + (e & 1);
         const bool valid = (kp >= lo || kp < keep) && kp <= pos;
-        s[nt][e] = valid ? s[nt][e] * p.scale_log2 : -INFINITY;
+        // (under a soft cap c: c tanh(s scale / c), in base-2 units)
+        const float sv = p.cap_out > 0.f ? p.cap_out * tanhf(s[nt][e] * p.cap_in) : s[nt][e] * p.scale_log2;
+        s[nt][e] = valid ? sv : -INFINITY;
         mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
       }
     float alpha[2];
@@ -464,7 +467,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
                                     const int* token_pos, const int* seq_slot, int n_tokens, int n_heads,
                                     int n_kv_heads, int head_dim, int window_kind, int window_size, float scale,
                                     int n_splits, float* part_o, float* part_ml, int* error_flag, int keep_first,
-                                    const float* sink, cudaStream_t stream) {
+                                    const float* sink, float softcap, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(cpi_attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_decode: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
@@ -475,7 +478,8 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
               "attention_decode: the cache must hold at least one page and be 16-byte aligned");
   dec::Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                 page_table, max_blocks, token_seq, token_pos, seq_slot, n_heads, n_kv_heads, window_kind, window_size,
-                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag, sink, keep_first > 0 ? keep_first : 0};
+                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag, sink, keep_first > 0 ? keep_first : 0,
+                softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f};
   // the cache as rows of head_dim features: a (page, head) tile is 64 consecutive rows
   CUtensorMap mk, mv;
   const uint64_t kv_rows = (uint64_t)n_pages * n_kv_heads * dec::PAGE;
@@ -565,5 +569,5 @@ extern "C" int cpi_attention_decode_noalloc(const void* q, void* out, const void
   float* part_ml = scratch + (long)n_tokens * n_heads * n_splits * head_dim;
   return cpi_attention_decode(q, out, k_cache, v_cache, n_pages, page_table, max_blocks, page_size, token_seq,
                               token_pos, seq_slot, n_tokens, n_heads, n_kv_heads, head_dim, window_kind, window_size,
-                              scale, n_splits, part_o, part_ml, nullptr, 0, nullptr, stream);
+                              scale, n_splits, part_o, part_ml, nullptr, 0, nullptr, 0.f, stream);
 }

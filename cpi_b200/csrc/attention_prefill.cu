@@ -48,6 +48,7 @@ struct Params {
   int* error_flag;
   const float* sink;                  // [NH] float32 or null: exp(sink[h]) joins the softmax denominator (no key, no value)
   int keep_first;                     // sliding window: a sequence's first positions stay visible to every later query
+  float cap_in, cap_out;              // soft cap c > 0 on the scaled scores: cap_in = scale / c, cap_out = c log2(e); else 0
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -118,6 +119,11 @@ __device__ __forceinline__ float exp2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// tanh(x) = 1 - 2 / (1 + e^(2x)) with the hardware's exponential and division (absolute error ~1e-7; the ends are exact:
+// e^(2x) = inf gives 1, 0 gives -1)
+__device__ __forceinline__ float tanh_fast(float x) {
+  return 1.0f - __fdividef(2.0f, 1.0f + exp2_fast(x * 2.885390081777927f));
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -404,7 +410,10 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t s_row = tmem_s + x * 128 + lane_addr, o_row = tmem_o + x * 128 + lane_addr;
     float m_ref = -1e30f, l_run = 0.f;                  // reference maximum of the exponentials; the row's sum
-    const float sc = p.scale_log2;                      // > 0: the maximum may be taken before scaling
+    // > 0: the maximum may be taken before scaling.  Under a soft cap c a raw score s first becomes tanh(s scale / c)
+    // (monotonic too) and the factor is c log2(e)
+    const bool capped = p.cap_out > 0.f;
+    const float sc = capped ? p.cap_out : p.scale_log2, cap_in = p.cap_in;
     // the union's last key tile holds positions beyond the newest one: their value rows are zeroed by the group
     // whose P V on that tile is issued first (A if it meets the tile, otherwise B)
     const bool zero_duty = x == 0 ? (kt1 - 1 >= kb_x[0] && kt1 - 1 < ke_x[0]) : !(kt1 - 1 >= kb_x[0] && kt1 - 1 < ke_x[0]);
@@ -450,7 +459,8 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
           if (no_mask) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              const float sv = __uint_as_float(raw[cc & 1][e]);
+              float sv = __uint_as_float(raw[cc & 1][e]);
+              if (capped) sv = tanh_fast(sv * cap_in);
               mx4[e & 3] = fmaxf(mx4[e & 3], sv);
               v[e] = exp2_fast(fmaf(sv, sc, nref));
             }
@@ -459,7 +469,8 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
             for (int e = 0; e < 32; ++e) {
               const int kp = key0 + cc * 32 + e;
               const bool in = kp <= qp && (kp >= lo || kp < keep);
-              const float sv = __uint_as_float(raw[cc & 1][e]);
+              float sv = __uint_as_float(raw[cc & 1][e]);
+              if (capped) sv = tanh_fast(sv * cap_in);
               if (in) mx4[e & 3] = fmaxf(mx4[e & 3], sv);
               v[e] = in ? exp2_fast(fmaf(sv, sc, nref)) : 0.f;
             }
@@ -562,7 +573,7 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
                                      const int* token_pos, const int* seq_slot, const int* tile_tok0,
                                      const int* tile_rows, int n_tiles, int n_tokens, int n_heads, int n_kv_heads,
                                      int head_dim, int window_kind, int window_size, float scale, int* error_flag,
-                                     const float* sink, int keep_first, cudaStream_t stream) {
+                                     const float* sink, int keep_first, float softcap, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
   CPI_REQUIRE(cpi_attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_prefill: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
@@ -576,7 +587,8 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
   if (tc::get_map_2d_bf16(v_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mv)) return 1;
   pre::Params p{(__nv_bfloat16*)out, page_table, max_blocks, token_pos, token_seq, seq_slot, tile_tok0, tile_rows,
                 n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag, sink,
-                keep_first > 0 ? keep_first : 0};
+                keep_first > 0 ? keep_first : 0, softcap > 0.f ? scale / softcap : 0.f,
+                softcap > 0.f ? softcap * 1.4426950408889634f : 0.f};
   dim3 grid(n_heads, n_tiles);
   const int halves = head_dim / 64;
   const int smem = halves * 128 * 128 * (2 + pre::kRingSlots);     // Q of both tiles, the ring of K and V tiles

@@ -729,7 +729,8 @@ def attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool
 
 
 def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
-                     n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, n_splits, sink=None, keep_first=0):
+                     n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, n_splits, sink=None, keep_first=0,
+                     softcap=0.0):
     """bfloat16 attention of independent tokens against the paged cache, keys split over `n_splits` blocks.
     `sink`: float32 [heads] whose exponentials join the softmax denominators.  `keep_first`: with a sliding window,
     a sequence's first positions that every later query still sees."""
@@ -752,7 +753,8 @@ def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq,
     _call("cpi_attention_decode", _p(q), _p(out), _p(k_cache), _p(v_cache), c_long(k_cache.shape[0]), _p(page_table),
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(T),
           c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale),
-          c_int(n_splits), _p(po), _p(pml), _p(tc_error_flag(q.device)), c_int(int(keep_first)), _p(sink), _stream())
+          c_int(n_splits), _p(po), _p(pml), _p(tc_error_flag(q.device)), c_int(int(keep_first)), _p(sink),
+          c_float(float(softcap or 0.0)), _stream())
 
 
 def latent_attention_supported(row: int, rank: int) -> bool:
@@ -812,7 +814,7 @@ def attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size) -> boo
 
 def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, tile_tok0,
                       tile_rows, *, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, sink=None,
-                      keep_first=0):
+                      keep_first=0, softcap=0.0):
     """bfloat16 attention of query tiles (<= PREFILL_TILE_ROWS consecutive tokens of one sequence each) on tcgen05.
     `sink`: float32 [heads] whose exponentials join the softmax denominators.  `keep_first`: as in `attention_decode`."""
     _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, tile_tok0, tile_rows, sink)
@@ -823,7 +825,7 @@ def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), _p(tile_tok0),
           _p(tile_rows), c_int(tile_tok0.numel()), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads),
           c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale), _p(tc_error_flag(q.device)),
-          _p(sink), c_int(int(keep_first)), _stream())
+          _p(sink), c_int(int(keep_first)), c_float(float(softcap or 0.0)), _stream())
 
 
 ROUTER_GATES = {"none": 0, "sigmoid": 1, "softmax_chosen": 2, "sigmoid_normed": 3}

@@ -361,7 +361,7 @@ def attend(q, att, k_cache, v_cache, table, page_size, batch, *, n_heads, n_kv_h
     nh, nkv, d, dv = n_heads, n_kv_heads, head_dim, value_dim
     wk = K.WINDOW_KINDS[window_kind]
     # the tensor-core kernels add nothing to a score and take keys and values of one size
-    tensor_cores = use_tensor_core_kernels and score_bias is None and dv == d and not softcap
+    tensor_cores = use_tensor_core_kernels and score_bias is None and dv == d
     if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
             and K.attention_decode_supported(nh, nkv, d, page_size)):
         # keys per sequence that the window lets through, at most (a bucketed bound: the split count
@@ -381,14 +381,14 @@ def attend(q, att, k_cache, v_cache, table, page_size, batch, *, n_heads, n_kv_h
         K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                            batch.seq_slot, n_heads=nh, n_kv_heads=nkv, head_dim=d,
                            window_kind=wk, window_size=window_size, scale=scale, n_splits=n_splits,
-                           sink=sink, keep_first=keep_first)
+                           sink=sink, keep_first=keep_first, softcap=softcap)
         return
     if (tensor_cores and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
             and K.attention_prefill_supported(nh, nkv, d, page_size)):
         K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=nh,
                             n_kv_heads=nkv, head_dim=d, window_kind=wk, window_size=window_size,
-                            scale=scale, sink=sink, keep_first=keep_first)
+                            scale=scale, sink=sink, keep_first=keep_first, softcap=softcap)
         return
     K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                         batch.seq_slot, n_heads=nh, n_kv_heads=nkv, head_dim=d, window_kind=wk,

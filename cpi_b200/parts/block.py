@@ -33,6 +33,7 @@ from ..csrc import lib as K
 from ..phases import phase
 from ..weights.store import TensorReq
 from .base import Block, register_block
+from .linear import single_cta_products
 
 
 @register_block("pre_norm")
@@ -199,6 +200,15 @@ class PostNormBlock(Block):
         ws.residual_copy = None if h is None else (x.data_ptr(), x.shape[0], x.shape[1], dtype)
 
     def run(self, layer, residual, batch, cache):
+        # The sublayers' products stay on the single-CTA tensor-core kernel.  With the two-SM kernel in these chains
+        # (a storing up product directly followed by a storing down product, the launches of this block between
+        # them and the next layer's) a prompt of 2,048 tokens at width 2,048 did not return in one run of a few;
+        # reading the kernels did not show why, and the single-CTA kernel ran the same prompts at the same speed
+        # (3.8 ms for four layers) every time, so that is what this block takes until the cause is known.
+        with single_cta_products():
+            self._run(layer, residual, batch, cache)
+
+    def _run(self, layer, residual, batch, cache):
         ws, x = layer.mixer_norm.ws, residual
         if x.dim() != 2:
             raise ValueError("post_norm: the block keeps one residual stream")

@@ -19,12 +19,24 @@ use_tensor_cores = True
 use_paired_kernel = True
 
 
+class single_cta_products:
+    """While entered, products with many tokens stay on the single-CTA kernel (a block whose chains of launches the
+    two-SM kernel is not cleared for wraps its sublayers in this).  Host-side routing only; nests."""
+    depth = 0
+
+    def __enter__(self):
+        single_cta_products.depth += 1
+
+    def __exit__(self, *exc):
+        single_cta_products.depth -= 1
+
+
 def project(a, w, out, mode=MODE_STORE, **kw):
     """Dense or grouped projection; see csrc/lib.py: gemm_simt for the keyword arguments."""
     if use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         # products with many tokens go to the two-SM kernel, dense or grouped (it refuses, launching nothing,
         # what it does not take: few tokens per group, features that are no multiple of 256, a row gather)
-        if use_paired_kernel and "a_rows" not in kw and kw.get("m_rows", a.shape[0]) >= 512 \
+        if use_paired_kernel and not single_cta_products.depth and "a_rows" not in kw and kw.get("m_rows", a.shape[0]) >= 512 \
                 and K.gemm_tc_pair(a, w, out, mode, **kw):
             return
         if K.gemm_tc(a, w, out, mode, **kw):

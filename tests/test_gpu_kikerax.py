@@ -589,6 +589,36 @@ def test_one_position_that_stands_out_for_a_left_side(tmp_path):
         r.check(b, {"x": toks}, TOL[dtype])
 
 
+def test_soft_cap_on_the_tensor_core_attention_kernels(tmp_path):
+    """Left sides with heads of 64 and of 128 under a tight and a loose soft cap: in bfloat16 these run on the
+    tensor-core attention kernels (a prompt of several query tiles, portions, decoding with key splits), and the result
+    is that of the general kernel and of the plain implementation; without the cap it would be another."""
+    from cpi_b200.parts import attention as A
+    cfg = V.model([V.layer(V.pair(4, 2, 64, 64, 2, 2, softcap=3.0, scale=0.5), V.dense(64)),
+                   V.layer(V.pair(2, 1, 128, 32, 1, 3, softcap=25.0, q_temp=(0.3, 100), scale=0.3), None)], width=128, vocab=60)
+    b = Built(cfg, 5, tmp_path)
+    toks = V.tokens(400, 60, 3)
+    no_cap = copy.deepcopy(cfg)
+    for L in no_cap["layers"]:
+        L["mixer"]["left"].pop("softcap")
+    assert (P.forward(no_cap, b.W, toks[:50]) - b.plain(toks[:50])).abs().max() > 1e-2
+    logits = {}
+    for tc in (True, False):
+        A.use_tensor_core_kernels = tc
+        try:
+            r = Run(b.engine("bfloat16", max_tokens=1024, max_seqs=2), record=False)
+            r.step([("x", toks[:300], range(0, 300, 7))])
+            r.step([("x", toks[300:360], range(60))])
+            for i in range(360, 400):
+                r.step([("x", toks[i:i + 1], [0])])
+            r.check(b, {"x": toks}, TOL["bfloat16"])
+            logits[tc] = r.logits["x"]
+        finally:
+            A.use_tensor_core_kernels = True
+    pos = sorted(logits[True])
+    assert err(torch.stack([logits[True][p] for p in pos]), torch.stack([logits[False][p] for p in pos]), rms=True) < TOL["bfloat16"]
+
+
 def test_other_constants_change_the_result_as_the_plain_implementation_says(tmp_path):
     base = V.model([V.layer(V.differential(4, 2, 8, 12, diff=0.4, chunk=9, rot_dims=4, base=100.0, scaling=(4.0, 16, 4.0, 0.5)),
                             V.moe(8, 2, 12, groups=(4, 2), shared=10)),
