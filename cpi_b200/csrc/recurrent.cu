@@ -567,13 +567,15 @@ __global__ void __launch_bounds__(1024) rglru_scan_kernel(RgLruParams p) {
   };
   if (runs > 1) {
     float A = 1.f, B = 0.f;
-    if (live)
+    if (live) {
+#pragma unroll 4
       for (int t = t_lo; t < t_hi; ++t) {
         float a, x;
         gate(t, a, x);
         B = fmaf(a, B, x);
         A *= a;
       }
+    }
     A_s[j][tx] = A; B_s[j][tx] = B;
     __syncthreads();
   }
@@ -583,6 +585,7 @@ __global__ void __launch_bounds__(1024) rglru_scan_kernel(RgLruParams p) {
   for (int jj = 0; jj < j; ++jj) S = fmaf(A_s[jj][tx], S, B_s[jj][tx]);
   const float* y = p.y + (size_t)tok0 * p.y_stride + c;
   TO* o = reinterpret_cast<TO*>(p.out) + (size_t)tok0 * p.out_stride + c;
+#pragma unroll 4
   for (int t = t_lo; t < t_hi; ++t) {
     float a, x;
     gate(t, a, x);

@@ -387,7 +387,8 @@ def test_choice_of_experts_from_the_best_groups(E, top, groups, keep, T):
         assert moved > 0
 
 
-@pytest.mark.parametrize("T,W,n,dt", [(5, 52, 2, torch.bfloat16), (3, 40, 1, torch.float32), (70, 256, 4, torch.bfloat16)])
+@pytest.mark.parametrize("T,W,n,dt", [(5, 52, 2, torch.bfloat16), (3, 40, 1, torch.float32), (70, 256, 4, torch.bfloat16),
+                                      (4, 37, 3, torch.bfloat16), (2, 8200, 2, torch.float32)])
 def test_norm_of_a_weighted_sum_enters_the_residual(T, W, n, dt):
     g = torch.Generator().manual_seed(T)
     ys, sc = [rn(g, T, W, std=2.0) for _ in range(n)], [0.6, 1.3, -0.4, 2.0][:n]
