@@ -8,6 +8,9 @@
 //                (with weights), a rotation of only the first elements of each head, or values of another size
 //                than keys, or a weightless RMS norm of every q and k head after the rotation; a block per token,
 //                float32 or bfloat16 rows in.
+//                Also: two score maps per head (second halves of the q and k rows to buffers of their own), values that
+//                are the projected keys, a query temperature, an amplitude on the rotation.
+//   head_post    what follows attention per token and head: a1 - lambda a2, its weightless norm, a sigmoid gate.
 //   attention    one block per (token, head): scores over the keys the window allows, softmax and the
 //                weighted sum of values in float32, keys visited in position order.  A position encoding
 //                that acts on the scores hands in a table: score(query at p, key at t) += bias[head][min(p - t,

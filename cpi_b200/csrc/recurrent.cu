@@ -15,6 +15,8 @@
 //                      A row decay may also be a_t = exp(-exp(A_log[head]) * softplus(z_t + bias)).  With `beta`
 //                      the update is the delta rule: after the decay, u_t = beta_t (v_t - S^T k_t), S += k_t u_t^T,
 //                      o_t = S^T q_t (the read-out sees the token's own write).
+//   rglru_scan         a gated linear recurrent unit with one state element per channel (see its own comment);
+//   block_major_rows   the equal parts of float32 rows laid out part by part, as the rows of a grouped product.
 //   head_unit          rows of heads made unit vectors in place: x / sqrt(sum(x^2) + eps) per head.
 //   gated_norm         out = norm_g(y * act(g)) * w  or  norm_g(y) * w * act(g): an RMS norm over equal parts
 //                      of a row (each part by its own mean square), gate before or after; act is silu or sigmoid.
@@ -516,11 +518,12 @@ static int dispatch_scan(const ScanParams& p, int n_seqs, int max_new, cudaStrea
 //   r = sigmoid(g_r + b_r), i = sigmoid(g_i + b_i)          (g: the gates' block-diagonal products, computed before)
 //   log a = -rate * softplus(lam) * r,   S_t = a S_{t-1} + sqrt(1 - a^2) * i * u_t,   out_t = S_t * gelu_tanh(y_t + b_y)
 // all in float32; 1 - a^2 is taken as -expm1(2 log a), which keeps its digits when a is close to one.  A block takes
-// 32 channels of one sequence.  A step of many tokens is cut into `blockDim.y` runs of consecutive tokens: every run
+// `blockDim.x` (32, or 16 when that fills the GPU better) neighbouring channels of one sequence.  A step of many tokens
+// is cut into `blockDim.y` runs of consecutive tokens: every run
 // is first scanned from a zero state (its product of decays and what it adds), the runs' results are chained in
 // shared memory, and a second pass repeats each run from its true entry state and writes the outputs.  A run of one
 // thread row (decode, short portions) is the recurrence as written.
-constexpr int RG_MAX_RUNS = 32;
+constexpr int RG_MAX_RUNS = 64;                   // with 16 channels a block; 32 with 32 (1,024 threads at most)
 
 struct RgLruParams {
   const float* gates; long gates_stride; // [blocks * T, 2 * block]: row b * T + t = block b's gate rows of token t (r, then i)
@@ -542,7 +545,7 @@ __global__ void __launch_bounds__(1024) rglru_scan_kernel(RgLruParams p) {
   pdl_launch_dependents();
   __shared__ float A_s[RG_MAX_RUNS][32], B_s[RG_MAX_RUNS][32];
   const int tx = threadIdx.x, j = threadIdx.y, runs = blockDim.y;
-  const int c = blockIdx.x * 32 + tx, s = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + tx, s = blockIdx.y;
   const bool live = c < p.width;
   float b_r = 0.f, b_i = 0.f, b_y = 0.f, rate = 0.f;
   if (live) {                                     // the channel's constants: no kernel writes them
@@ -636,16 +639,18 @@ extern "C" int cpi_rglru_scan(const float* gates, long gates_stride, const void*
   CPI_REQUIRE(n_seqs <= 65535, "rglru_scan: too many sequences in one step (%d)", n_seqs);
   RgLruParams p{gates, gates_stride, r_bias, i_bias, lam, y_bias, small_dtype, u, u_stride, y, y_stride, state, out,
                 out_stride, seq_slot, seq_tok0, seq_new, n_tokens, width, block, rate};
-  // runs of at least 16 tokens, as many as fill the GPU twice over, at most RG_MAX_RUNS
-  int runs = 1;
+  // runs of at least 16 tokens, as many as fill the GPU twice over; 16 channels a block (64-byte segments) where 32
+  // would leave SMs without a block
+  int runs = 1, ch = 32;
   if (max_new >= 32) {
-    const int blocks = n_seqs * ((width + 31) / 32);
-    runs = (2 * sm_count() * 2048 / 32 + blocks - 1) / blocks;
+    if (n_seqs * ((width + 31) / 32) < 2 * sm_count()) ch = 16;
+    const int blocks = n_seqs * ((width + ch - 1) / ch);
+    runs = (2 * sm_count() * 2048 / ch + blocks - 1) / blocks;
     if (runs > max_new / 16) runs = max_new / 16;
-    if (runs > RG_MAX_RUNS) runs = RG_MAX_RUNS;
+    if (runs > 1024 / ch) runs = 1024 / ch;
     if (runs < 1) runs = 1;
   }
-  const dim3 grid((width + 31) / 32, n_seqs), block_dim(32, runs);
+  const dim3 grid((width + ch - 1) / ch, n_seqs), block_dim(ch, runs);
   CPI_DISPATCH_DTYPE(out_dtype, TO, cpi::launch_pdl(rglru_scan_kernel<TO>, grid, block_dim, 0, stream, p));
   return check_launch("rglru_scan");
 }
