@@ -275,8 +275,14 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   const TI* src = reinterpret_cast<const TI*>(p.qkv) + (size_t)t * p.qkv_stride;
   const int pos = p.token_pos[t];
   const float temp = p.temperature ? 1.0f + p.attn_scale * logf(floorf(((float)pos + 1.0f) / p.floor_scale) + 1.0f) : 1.0f;
+  // a step of few tokens is also cut along the heads: block (t, y) takes the q and k heads [h0, h1) of the row and the
+  // value heads [vh0, vh1) (one slice when the norm runs over the whole projection)
+  const int heads_all = (nq + nk) / D, v_heads = nv / DV;
+  const int h0 = (int)((long)heads_all * blockIdx.y / gridDim.y), h1 = (int)((long)heads_all * (blockIdx.y + 1) / gridDim.y);
+  const int e0 = h0 * D, e1 = h1 * D;
+  const int v0 = (int)((long)v_heads * blockIdx.y / gridDim.y) * DV, v1 = (int)((long)v_heads * (blockIdx.y + 1) / gridDim.y) * DV;
   float ssq = 0.f, ssk = 0.f;
-  for (int i = tid; i < nq + nk; i += blockDim.x) {
+  for (int i = e0 + tid; i < e1; i += blockDim.x) {
     float x = to_f32(src[i]);
     if (p.bias) x += load_any(p.bias, p.bias_dtype, i);
     row_s[i] = x;
@@ -313,7 +319,7 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   float* rot_s = row_s + nq + nk;                        // head_norm: the rotated row, then one factor per head
   float* inv_s = rot_s + nq + nk;
   if (p.head_norm == 1) {
-    for (int i = tid; i < nq + nk; i += blockDim.x) {
+    for (int i = e0 + tid; i < e1; i += blockDim.x) {
       const int e = i < nq ? i : i - nq, d = e % D;
       float x = row_s[i];
       if (p.inv_freq && d < p.rot_dims) {
@@ -328,15 +334,15 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
       rot_s[i] = x;
     }
     __syncthreads();
-    const int n_heads_all = (nq + nk) / D, warp = tid >> 5, lane = tid & 31;
-    for (int hd = warp; hd < n_heads_all; hd += blockDim.x >> 5) {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int hd = h0 + warp; hd < h1; hd += blockDim.x >> 5) {
       float ss = 0.f;
       for (int d = lane; d < D; d += 32) ss = fmaf(rot_s[hd * D + d], rot_s[hd * D + d], ss);
       ss = warp_sum(ss);
       if (lane == 0) inv_s[hd] = 1.0f / sqrtf(ss / (float)D + p.norm_eps);
     }
     __syncthreads();
-    for (int i = tid; i < nq + nk; i += blockDim.x) {
+    for (int i = e0 + tid; i < e1; i += blockDim.x) {
       const bool is_q = i < nq;
       const int e = is_q ? i : i - nq;
       const float x = rot_s[i] * inv_s[i / D];
@@ -347,15 +353,15 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
   if (p.head_norm == 2) {
     // every head by its own root mean square, times the weight of its element, and then the rotation
     float* inv_h = row_s + nq + nk;
-    const int n_heads_all = (nq + nk) / D, warp = tid >> 5, lane = tid & 31;
-    for (int hd = warp; hd < n_heads_all; hd += blockDim.x >> 5) {
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int hd = h0 + warp; hd < h1; hd += blockDim.x >> 5) {
       float ss = 0.f;
       for (int d = lane; d < D; d += 32) ss = fmaf(row_s[hd * D + d], row_s[hd * D + d], ss);
       ss = warp_sum(ss);
       if (lane == 0) inv_h[hd] = 1.0f / sqrtf(ss / (float)D + p.norm_eps);
     }
     __syncthreads();
-    for (int i = tid; i < nq + nk; i += blockDim.x) {
+    for (int i = e0 + tid; i < e1; i += blockDim.x) {
       const bool is_q = i < nq;
       const int e = is_q ? i : i - nq;
       const int hd = e / D, d = e % D;
@@ -380,7 +386,7 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
       else store_k(e, x);
     }
   }
-  for (int i = tid; i < (p.head_norm ? 0 : nq + nk); i += blockDim.x) {
+  for (int i = e0 + tid; i < (p.head_norm ? 0 : e1); i += blockDim.x) {
     const bool is_q = i < nq;
     const int e = is_q ? i : i - nq;
     const int hd = e / D, d = e % D;
@@ -404,10 +410,11 @@ __global__ void __launch_bounds__(1024) qkv_prepare_kernel(QkvPrepParams p) {
     if (is_q) store_q(i, x);
     else store_k(e, x);
   }
-  for (int i = tid; i < nv; i += blockDim.x) {
+  for (int i = v0 + tid; i < v1; i += blockDim.x) {
     float x;
-    if (p.v_from_k) {
-      x = row_s[nq + i];                                 // the key as projected, its bias added, before the norm
+    if (p.v_from_k) {                                    // the key as projected, its bias added, before the norm
+      x = to_f32(src[nq + i]);
+      if (p.bias) x += load_any(p.bias, p.bias_dtype, nq + i);
     } else {
       x = to_f32(src[nq + nk + i]);
       if (p.bias) x += load_any(p.bias, p.bias_dtype, nq + nk + i);
@@ -651,13 +658,21 @@ extern "C" int cpi_qkv_prepare(const void* qkv, int in_dtype, long qkv_stride, c
   const size_t n_norms = (size_t)maps * (n_heads + n_kv_heads);
   const size_t smem = (head_norm == 1 ? 2 * row + n_norms : head_norm == 2 ? row + n_norms : row) * sizeof(float);
   CPI_REQUIRE(smem <= 200 * 1024, "qkv_prepare: a q and k row of %zu bytes does not fit in shared memory", smem);
-  // with few tokens the blocks are large (a few elements per thread); a prompt has blocks enough
-  const int threads = n_tokens <= 2 * sm_count() ? 1024 : 256;
+  // with few tokens a row is cut along its heads into slices, enough blocks for two per SM (a norm over the whole
+  // projection keeps a row in one block, which is then large); a prompt has blocks enough
+  const int heads_all = maps * (n_heads + (write_kv ? n_kv_heads : 0));
+  int slices = 1;
+  if (!norm_whole && n_tokens < 2 * sm_count()) {
+    slices = (2 * sm_count() + n_tokens - 1) / n_tokens;
+    if (slices > (heads_all + 1) / 2) slices = (heads_all + 1) / 2;
+    if (slices < 1) slices = 1;
+  }
+  const int threads = slices == 1 && n_tokens <= 2 * sm_count() ? 1024 : 256;
 #define CPI_PREP(TI, TO)                                                                                       \
   do {                                                                                                         \
     auto kern = qkv_prepare_kernel<TI, TO>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    cpi::launch_pdl(kern, dim3(n_tokens), dim3(threads), smem, stream, p);                                       \
+    cpi::launch_pdl(kern, dim3(n_tokens, slices), dim3(threads), smem, stream, p);                                       \
   } while (0)
   if (in_dtype == kF32 && out_dtype == kF32) CPI_PREP(float, float);
   else if (in_dtype == kF32 && out_dtype == kBF16) CPI_PREP(float, __nv_bfloat16);
